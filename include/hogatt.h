@@ -1,0 +1,175 @@
+/*
+ * hogatt.h -- C ABI of the B200-native Hogwild! fragmented-KV attention library
+ * (libhogatt_b200.so).
+ *
+ * The reference project has no C ABI of its own: its torch operators (src/binding.cu:360-386)
+ * call C++ templates (src/kernels/kernel_v21.cuh:951-1086, src/rope.cuh:54-62) with raw pointers
+ * and a `Shape` POD (src/common.h:5-20).  The functions below are that same layer, cut at the
+ * raw-pointer level, so that a binding in any language can replace the reference launchers one
+ * for one.  Each entry point names the reference interface it stands in for.
+ *
+ * Conventions
+ *   - Plain C types only.  Every pointer marked "device" must be dereferenceable by the GPU that is
+ *     current on the calling thread; every pointer marked "host" is read during the call only.
+ *   - All tensors are dense and row-major in the stated shape (the reference checks
+ *     `is_contiguous()` on each of them, src/binding.cu:51-97).  Key/value rows and query rows must
+ *     start on a 16-byte boundary (the reference's 16-byte vector loads need the same).
+ *   - Nothing here allocates, frees or synchronises (except where an entry point says otherwise):
+ *     scratch memory comes from the caller (`hogatt_workspace_bytes`), work is enqueued on the
+ *     stream given, and the call returns as soon as the launches are queued.  Calls are
+ *     re-entrant and may be captured into a CUDA graph.
+ *   - Return value: 0 on success, a negative `hogatt_status` otherwise; nothing is launched when
+ *     an error is returned.  Unsupported shapes are an error (the reference prints a message and
+ *     reports success with the output untouched, src/kernels/kernel_v21.cuh:992-995).
+ *   - A row that can see no key at all produces zeros (as the reference kernel does,
+ *     src/kernels/kernel_v21.cuh:238-245).
+ */
+#ifndef HOGATT_H_
+#define HOGATT_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define HOGATT_ABI_VERSION 1
+#define HOGATT_MAX_FRAGMENTS 128   /* fragment table travels by value in the kernel arguments */
+
+typedef struct CUstream_st* hogatt_stream_t;   /* == cudaStream_t */
+
+typedef enum hogatt_dtype {
+    HOGATT_F32 = 0,
+    HOGATT_F16 = 1,
+    HOGATT_BF16 = 2
+} hogatt_dtype;
+
+typedef enum hogatt_status {
+    HOGATT_OK = 0,
+    HOGATT_ERR_NULL_POINTER = -1,
+    HOGATT_ERR_BAD_SHAPE = -2,          /* non-positive dims, Hq not a multiple of Hkv, rotary_dim odd or > E */
+    HOGATT_ERR_UNSUPPORTED_HEAD_DIM = -3,
+    HOGATT_ERR_UNSUPPORTED_DTYPE = -4,
+    HOGATT_ERR_TOO_MANY_FRAGMENTS = -5,
+    HOGATT_ERR_MISALIGNED = -6,
+    HOGATT_ERR_WORKSPACE_TOO_SMALL = -7,
+    HOGATT_ERR_CUDA = -8,               /* a CUDA runtime call failed; see hogatt_last_cuda_error() */
+    HOGATT_ERR_BAD_KERNEL_CHOICE = -9,
+    HOGATT_ERR_TOO_LARGE = -10
+} hogatt_status;
+
+/* Which device code runs.  AUTO picks the tensor-core kernel for f16/bf16 with E == Ev in {64, 128}
+ * and the FMA kernel for everything else (fp32, other head sizes). */
+typedef enum hogatt_kernel_choice {
+    HOGATT_KERNEL_AUTO = 0,
+    HOGATT_KERNEL_FMA = 1,
+    HOGATT_KERNEL_MMA = 2
+} hogatt_kernel_choice;
+
+/*
+ * One call of the fragment attention op.  Field names follow the reference's `Shape`
+ * (src/common.h:5-20) and operator arguments (src/binding.cu:363-367).
+ */
+typedef struct hogatt_problem {
+    int32_t F;            /* fragments                       */
+    int32_t W;            /* workers                         */
+    int32_t Hq;           /* query heads                     */
+    int32_t Hkv;          /* key/value heads, Hq % Hkv == 0  */
+    int32_t E;            /* qk head size                    */
+    int32_t Ev;           /* v head size                     */
+    int32_t S;            /* query tokens per worker         */
+    int32_t rotary_dim;   /* R: leading channels that are rotated (ignored when cosines == NULL) */
+    int32_t dtype;        /* hogatt_dtype of out, rq, queries, keys, values */
+    float   scale;        /* softmax scale applied to q.k    */
+
+    void*        out;      /* device [W,Hq,S,Ev]                                              */
+    void*        rq;       /* device [F,W,Hq,S,E] or NULL: rotated queries, written when given */
+    const void*  queries;  /* device: [W,Hq,S,E] un-rotated when cosines != NULL,
+                                      [F,W,Hq,S,E] already rotated when cosines == NULL        */
+    const float* cosines;  /* device [F,W,S,R] fp32 or NULL                                   */
+    const float* sines;    /* device [F,W,S,R] fp32 or NULL                                   */
+    const int32_t* locations;         /* device [F,W,S]: key l of fragment f is visible to (w,s)
+                                         iff l <= locations[f,w,s]                            */
+    const int32_t* fragment_lengths;  /* device [F] or NULL: visible length of each fragment;
+                                         NULL means fragment_rows[f]                          */
+
+    const void* const* key_fragments;    /* host array of F device pointers, each [Hkv, rows_f, E]  */
+    const void* const* value_fragments;  /* host array of F device pointers, each [Hkv, rows_f, Ev] */
+    const int32_t*     fragment_rows;    /* host array of F ints: rows_f, the token extent of the
+                                            tensors (their head stride is rows_f * E)           */
+
+    void*   workspace;        /* device scratch, >= hogatt_workspace_bytes() bytes, 256-byte aligned */
+    size_t  workspace_bytes;
+    int32_t* device_status;   /* device int or NULL: kernels OR a nonzero code into it when a bounded
+                                 wait inside a kernel gives up (never expected in normal operation) */
+    int32_t kernel;           /* hogatt_kernel_choice */
+    int32_t max_ctas;         /* 0 = one CTA per SM; otherwise caps the persistent grid (testing)   */
+} hogatt_problem;
+
+/* ABI version compiled into the library (== HOGATT_ABI_VERSION of the header it was built from). */
+int hogatt_abi_version(void);
+
+/* Static text for a hogatt_status. */
+const char* hogatt_status_string(int status);
+
+/* The last cudaError_t seen by this thread inside the library (0 if none), for HOGATT_ERR_CUDA. */
+int hogatt_last_cuda_error(void);
+
+/*
+ * Scratch bytes hogatt_sdpa_launch / hogatt_fused_launch need for this problem on the current
+ * device (split-K partial sums and their softmax statistics).  Only the dims, dtype, kernel and
+ * max_ctas fields are read.  Returns 0 for an invalid problem.
+ * Stands in for the grow-only static workspace of src/kernels/kernel_v21.cuh:969-980.
+ */
+size_t hogatt_workspace_bytes(const hogatt_problem* p);
+
+/*
+ * Attention over fragments with queries that are already rotated: problem.queries is
+ * [F,W,Hq,S,E], cosines/sines/rq must be NULL.
+ * Replaces v21::hogwild_attention_gpu (src/kernels/kernel_v21.cuh:951-996) as called from the
+ * `hogwild_sdpa` operator (src/binding.cu:39-108,255-267).
+ */
+int hogatt_sdpa_launch(const hogatt_problem* p, hogatt_stream_t stream);
+
+/*
+ * Query RoPE per fragment fused into the attention prologue: problem.queries is [W,Hq,S,E],
+ * cosines/sines are given; when rq != NULL the rotated queries are also written out.
+ * Replaces the composition rope_gpu + v21::hogwild_attention_gpu of the `hogwild_fused` operator
+ * (src/binding.cu:324-340).
+ */
+int hogatt_fused_launch(const hogatt_problem* p, hogatt_stream_t stream);
+
+/*
+ * rq[f,w,h,s,:] = rope(queries[w,h,s,:], cosines[f,w,s,:], sines[f,w,s,:]) with the rotate-half
+ * pairing, channels >= R copied.  All pointers device.
+ * Replaces rope_gpu (src/rope.cuh:54-62) of the `hogwild_rope` operator (src/binding.cu:217-253).
+ */
+int hogatt_rope_launch(void* rq, const void* queries, const float* cosines, const float* sines,
+                       int32_t F, int32_t W, int32_t Hq, int32_t S, int32_t E, int32_t rotary_dim,
+                       int32_t dtype, hogatt_stream_t stream);
+
+/*
+ * Host-only description of how a problem is cut into work for the persistent grid; no GPU needed.
+ * `visible_rows[f]` is the number of leading keys of fragment f that some query row can see.
+ * Fills: plan[0] = tokens per tile, plan[1] = rows per row block, plan[2] = row blocks,
+ * plan[3] = tiles per (row block, kv head) unit, plan[4] = units, plan[5] = CTAs that get work,
+ * plan[6] = partial-result slots per unit, plan[7] = kernel chosen (hogatt_kernel_choice).
+ * Used by the tests of the split-K decomposition; has no reference counterpart (the reference
+ * derives `splits` inline, src/kernels/kernel_v21.cuh:957-964).
+ */
+int hogatt_plan_describe(const hogatt_problem* p, const int32_t* visible_rows, int32_t num_sms,
+                         int32_t plan[8]);
+
+/*
+ * For the decomposition above: the half-open range of global tile indices CTA `cta` walks
+ * (range[0], range[1]) and, for unit `unit`, the first CTA that touches it and how many do
+ * (range[2], range[3]).  Host-only.
+ */
+int hogatt_plan_ranges(int32_t tiles_per_unit, int32_t units, int32_t ctas, int32_t cta, int32_t unit,
+                       int64_t range[4]);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HOGATT_H_ */
