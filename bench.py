@@ -1,0 +1,389 @@
+#!/usr/bin/env python
+"""Benchmark of the Hogwild! fragmented-KV attention op on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload target|cfg2|cfg3|cfg4] [--impl reference]
+
+One *step* is one decode step's worth of attention: ``--layers`` (default 32) calls of the fused
+RoPE + attention op, one per transformer layer, each layer with its own KV fragments.  The layers'
+KV sets together (2 GiB for the default workload) are far larger than the 126 MB L2, so every call
+reads its KV cold from HBM.  ``value`` is the achieved algorithmic bandwidth of the whole job
+(KV once + Q + O bytes of every call / time); ``us_per_call`` is the time of one call.
+
+With ``--gpus N`` (launched under torchrun, one rank per GPU) the same workload is sharded by KV
+head; every rank computes its heads and the outputs are all-gathered over NCCL.  Timing is on the
+device (CUDA events on the launching stream), max over ranks.
+
+``--impl reference`` times the reference's CPU algorithm (its PyTorch path, restated in
+``oracle/``) on the host cores for the same workload, metric and unit.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from inference_lib_b200 import workloads as wl  # noqa: E402
+
+METRIC = "hogwild attn achieved HBM TB/s (us/call in us_per_call)"
+UNIT = "TB/s"
+NOMINAL_HBM_GBS = 8000.0
+FALLBACK_HBM_GBS = 6650.0
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as fh:
+            return float(json.load(fh)["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples while the timed region runs (read-only query)."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.gpu), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.05)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            parts = [x.strip() for x in ln.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1])); mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------
+# workload
+# ------------------------------------------------------------------------------------------------
+def layer_problems(name: str, layers: int, rank: int, world: int, device):
+    """``layers`` device-resident problems.  Layer 0 is the seeded problem itself; the other layers
+    reuse its queries and metadata with their own KV memory (layer i's KV = layer 0's values rolled
+    by i rows), so the layers occupy distinct HBM without spending minutes in the CPU generator."""
+    base = wl.baseline_problem(name)
+    if world > 1:
+        base = base.shard(rank, world)
+    d0 = base.to(device)
+    probs = [d0]
+    for i in range(1, layers):
+        keys = [torch.roll(k, shifts=i, dims=2) for k in d0.keys]
+        vals = [torch.roll(v, shifts=i, dims=2) for v in d0.values]
+        probs.append(wl.Problem(**{**d0.__dict__, "keys": keys, "values": vals}))
+    return base, probs
+
+
+class CabiCall:
+    """One pre-bound C-ABI call (pointers fixed, so the step can be captured into a CUDA graph)."""
+
+    def __init__(self, p: wl.Problem, device, workspace=None, want_rq=True):
+        from inference_lib_b200 import _cabi
+        self._cabi = _cabi
+        self.out = torch.empty((p.W, p.Hq, p.S, p.Ev), dtype=p.dtype, device=device)
+        self.rq = torch.empty((p.F, p.W, p.Hq, p.S, p.E), dtype=p.dtype, device=device) if want_rq else None
+        self.bp = _cabi.bind(out=self.out, queries=p.queries, locations=p.locations, keys=p.keys, values=p.values,
+                             scale=p.scale, fragment_lengths=p.fragment_lengths, cos=p.cos, sin=p.sin, rq=self.rq)
+        need = _cabi.workspace_bytes(self.bp)
+        if need == 0:
+            raise RuntimeError("libhogatt_b200 refused the workload")
+        self.ws = workspace if workspace is not None else torch.empty(need + 256, dtype=torch.uint8, device=device)
+        off = (-self.ws.data_ptr()) % 256
+        self.bp.struct.workspace, self.bp.struct.workspace_bytes = self.ws.data_ptr() + off, need
+
+    def launch(self, stream: int):
+        rc = self._cabi.launch(self.bp, stream)
+        if rc != 0:
+            raise RuntimeError(f"hogatt launch failed: {self._cabi.status_string(rc)}")
+
+
+def time_steps(step_fn, steps: int, warmup: int, barrier):
+    for _ in range(warmup):
+        step_fn()
+    torch.cuda.synchronize()
+    barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step_fn()
+    e1.record()
+    torch.cuda.synchronize()
+    barrier()
+    return e0.elapsed_time(e1) / 1e3      # seconds
+
+
+def run_ours(args):
+    rank = int(os.environ.get("RANK", 0)); world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device; there is no CPU fallback for the op")
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+    barrier = (lambda: dist.barrier()) if dist else (lambda: None)
+
+    from inference_lib_b200 import _build
+    _build.build_all()
+    full, probs = layer_problems(args.workload, args.layers, rank, world, device)
+    whole = wl.baseline_problem(args.workload) if world > 1 else full
+    bytes_per_call = whole.algorithmic_bytes()                   # whole job, all ranks
+    calls = [CabiCall(p, device) for p in probs]
+    stream = torch.cuda.Stream(device)
+
+    gathered = None
+    if dist:
+        gathered = [torch.empty((world,) + tuple(c.out.shape), dtype=c.out.dtype, device=device) for c in calls]
+
+    def step_body(sid):
+        for i, c in enumerate(calls):
+            c.launch(sid)
+            if dist:
+                dist.all_gather_into_tensor(gathered[i], c.out)
+
+    launches_per_step = 2 * len(calls)
+
+    # the step is launch-bound from Python, so replay it as a CUDA graph (single-GPU; NCCL calls stay eager)
+    graph = None
+    with torch.cuda.stream(stream):
+        step_body(stream.cuda_stream)
+        torch.cuda.synchronize()
+        if not dist and not args.no_graph:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                step_body(torch.cuda.current_stream().cuda_stream)
+
+        def step():
+            if graph is not None:
+                graph.replay()
+            else:
+                step_body(torch.cuda.current_stream().cuda_stream)
+
+        sampler = ClockSampler(local)
+        if rank == 0:
+            sampler.start()
+        secs = time_steps(step, args.steps, args.warmup, barrier)
+        clocks = sampler.stop() if rank == 0 else None
+
+        # attention-only time at N > 1 (no gather), for the split the scaling discussion needs
+        secs_attn = None
+        if dist:
+            def step_attn():
+                for c in calls:
+                    c.launch(torch.cuda.current_stream().cuda_stream)
+            secs_attn = time_steps(step_attn, args.steps, args.warmup, barrier)
+
+        # isolated, cold call: one launch between events, L2 flushed by a 256 MiB write before it
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+        iso = []
+        for i in range(12):
+            flush.fill_(i)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); calls[i % len(calls)].launch(torch.cuda.current_stream().cuda_stream); e1.record()
+            torch.cuda.synchronize()
+            iso.append(e0.elapsed_time(e1) * 1e3)
+        iso_us = statistics.median(iso[2:])
+
+    t = torch.tensor([secs, secs_attn or 0.0], dtype=torch.float64, device=device)
+    if dist:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    secs, secs_attn = float(t[0]), float(t[1])
+    n_calls = args.steps * len(calls)
+    us_per_call = secs / n_calls * 1e6
+    value = bytes_per_call * n_calls / secs / 1e12
+
+    e2e = measure_e2e(args, full, device, dist, world) if True else None
+
+    if rank != 0:
+        if dist:
+            dist.destroy_process_group()
+        return
+    peak, peak_src = measured_peak()
+    per_gpu_bytes = bytes_per_call / world
+    achieved = per_gpu_bytes / ((secs_attn or secs) / n_calls) / 1e9
+    line = {
+        "metric": METRIC, "value": round(value, 4), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(secs / args.steps * 1e3, 5), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": str(full.dtype).replace("torch.", "") + " in, fp32 accumulate",
+        "data": "synthetic (seeded N(0,1) q/k/v, keys pre-rotated)",
+        "config": {"workload": args.workload, **{k: v for k, v in full.meta.items() if k not in ("seed",)},
+                   "layers_per_step": len(calls), "kv_bytes_resident": int(sum(p.algorithmic_bytes() for p in probs)),
+                   "l2": "inputs larger than L2 (one distinct KV set per layer); isolated call uses an L2 flush",
+                   "parallelism": f"kv-head shard x{world}" if world > 1 else "single GPU",
+                   "cuda_graph": graph is not None},
+        "us_per_call": round(us_per_call, 3),
+        "us_per_call_isolated_cold": round(iso_us, 3),
+        "pct_of_nominal_8TBps": round(100 * value * 1e3 / (NOMINAL_HBM_GBS * world), 2),
+        "gpu_launches": launches_per_step * args.steps,
+        "clocks": clocks,
+        "e2e": e2e,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+                     "frac": round(achieved / peak, 4), "traffic": None, "peak_source": peak_src,
+                     "kernel": "mma_attention_kernel (+ merge_kernel in the same interval)",
+                     "bytes_per_launch": int(per_gpu_bytes)},
+    }
+    if secs_attn:
+        line["attention_only_us_per_call"] = round(secs_attn / n_calls * 1e6, 3)
+    if world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(args.workload, budget_s=20.0)
+    print(json.dumps(line), flush=True)
+    if dist:
+        dist.destroy_process_group()
+
+
+def measure_e2e(args, p: wl.Problem, device, dist, world):
+    """The same metric through the public Python API with HOST inputs: every call copies the step's
+    tensors (queries, tables, locations and the KV fragments) from pinned host memory, runs
+    ``hogwild_fused`` and reads the output back."""
+    import inference_lib_b200.attention as A
+    pin = lambda t: t.contiguous().pin_memory()
+    hq, hcos, hsin, hloc, hlen = pin(p.queries), pin(p.cos), pin(p.sin), pin(p.locations), pin(p.fragment_lengths)
+    hk, hv = [pin(k) for k in p.keys], [pin(v) for v in p.values]
+    dq, dcos, dsin, dloc, dlen = [torch.empty_like(t, device=device) for t in (hq, hcos, hsin, hloc, hlen)]
+    dk, dv = [torch.empty_like(t, device=device) for t in hk], [torch.empty_like(t, device=device) for t in hv]
+    rq = torch.empty((p.F, p.W, p.Hq, p.S, p.E), dtype=p.dtype, device=device)
+    out = torch.empty((p.W, p.Hq, p.S, p.Ev), dtype=p.dtype, device=device)
+    hout = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+    gathered = torch.empty((world,) + tuple(out.shape), dtype=out.dtype, device=device) if dist else None
+    h2d = sum(t.numel() * t.element_size() for t in [hq, hcos, hsin, hloc, hlen] + hk + hv)
+    d2h = hout.numel() * hout.element_size()
+
+    def call():
+        for d, h in zip([dq, dcos, dsin, dloc, dlen] + dk + dv, [hq, hcos, hsin, hloc, hlen] + hk + hv):
+            d.copy_(h, non_blocking=True)
+        A.hogwild_fused(dq, dloc, dk, dv, p.scale, dlen, dcos, dsin, rotated_queries=rq, out=out)
+        if dist:
+            dist.all_gather_into_tensor(gathered, out)
+        hout.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(3):
+        call()
+    torch.cuda.synchronize()
+    if dist:
+        dist.barrier()
+    n = 10
+    t0 = time.perf_counter()
+    for _ in range(n):
+        call()
+    dt = (time.perf_counter() - t0) / n
+    tt = torch.tensor([dt], dtype=torch.float64, device=device)
+    if dist:
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+    dt = float(tt[0])
+    whole_bytes = wl.baseline_problem(args.workload).algorithmic_bytes() if world > 1 else p.algorithmic_bytes()
+    return {"value": round(whole_bytes / dt / 1e12, 5), "unit": UNIT, "us_per_call": round(dt * 1e6, 1),
+            "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+            "what": "pinned host -> device copy of q/cos/sin/loc/lengths and all KV fragments, hogwild_fused, output back to host"}
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU legs (the only places that run the oracle)
+# ------------------------------------------------------------------------------------------------
+def cpu_baseline(workload: str, budget_s: float, reps_cap: int = 5):
+    from oracle import hogwild_oracle as oracle
+    torch.set_num_threads(os.cpu_count() or 1)
+    p = wl.baseline_problem(workload)
+    run = lambda: oracle.fused(p.queries, p.cos, p.sin, p.locations, p.keys, p.values, p.scale)
+    t0 = time.perf_counter(); run(); first = time.perf_counter() - t0
+    reps = max(1, min(reps_cap, int(budget_s / max(first, 1e-3)) - 1))
+    ts = []
+    for _ in range(reps):
+        t0 = time.perf_counter(); run(); ts.append(time.perf_counter() - t0)
+    dt = statistics.median(ts)
+    return {"value": round(p.algorithmic_bytes() / dt / 1e12, 7), "unit": UNIT, "us_per_call": round(dt * 1e6, 1),
+            "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{reps} full calls of the '{workload}' problem (one layer) after 1 warm-up, median"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", 0))
+    if rank != 0:
+        return
+    from oracle import hogwild_oracle as oracle
+    torch.set_num_threads(os.cpu_count() or 1)
+    p = wl.baseline_problem(args.workload)
+    run = lambda: oracle.fused(p.queries, p.cos, p.sin, p.locations, p.keys, p.values, p.scale)
+    steps, warmup = min(args.steps, 8), min(args.warmup, 2)      # each step is one call: a bounded sample
+    for _ in range(warmup):
+        run()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        run()
+    dt = (time.perf_counter() - t0) / steps
+    value = p.algorithmic_bytes() / dt / 1e12
+    line = {
+        "impl": "reference", "metric": METRIC, "value": round(value, 7), "unit": UNIT,
+        "n_gpus": int(os.environ.get("WORLD_SIZE", 1)), "steps": steps, "warmup": warmup,
+        "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": str(p.dtype).replace("torch.", "") + " in, fp32 accumulate", "data": "synthetic (seeded N(0,1) q/k/v, keys pre-rotated)",
+        "config": {"workload": args.workload, **{k: v for k, v in p.meta.items() if k != "seed"},
+                   "step": "one call of the op on one layer's tensors (bounded sample of the 32-layer step)"},
+        "us_per_call": round(dt * 1e6, 1),
+        "cpu_baseline": {"value": round(value, 7), "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": f"{steps} calls of the '{args.workload}' problem, reference PyTorch algorithm restated in oracle/"},
+        "e2e": {"value": round(value, 7), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=300)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="target", choices=["target", "cfg2", "cfg3", "cfg4"])
+    ap.add_argument("--layers", type=int, default=32)
+    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.workload == "cfg4":
+        args.layers = min(args.layers, 4)          # 570 MB of KV per layer
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

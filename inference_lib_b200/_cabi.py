@@ -1,0 +1,133 @@
+"""ctypes view of the C ABI in ``include/hogatt.h`` (``libhogatt_b200.so``).
+
+Used by the tests and the benchmark to drive the library exactly as a non-torch host would:
+raw device pointers, a caller-provided workspace and a stream handle.  There is no fallback: if
+the shared object is missing, :func:`load` raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from typing import Optional, Sequence
+
+PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(PKG, "libhogatt_b200.so")
+
+F32, F16, BF16 = 0, 1, 2
+KERNEL_AUTO, KERNEL_FMA, KERNEL_MMA = 0, 1, 2
+MAX_FRAGMENTS = 128
+
+EXPORTS = ["hogatt_abi_version", "hogatt_status_string", "hogatt_last_cuda_error", "hogatt_workspace_bytes",
+           "hogatt_sdpa_launch", "hogatt_fused_launch", "hogatt_rope_launch", "hogatt_plan_describe",
+           "hogatt_plan_ranges"]
+
+
+class Problem(C.Structure):
+    _fields_ = [
+        ("F", C.c_int32), ("W", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("E", C.c_int32),
+        ("Ev", C.c_int32), ("S", C.c_int32), ("rotary_dim", C.c_int32), ("dtype", C.c_int32), ("scale", C.c_float),
+        ("out", C.c_void_p), ("rq", C.c_void_p), ("queries", C.c_void_p), ("cosines", C.c_void_p),
+        ("sines", C.c_void_p), ("locations", C.c_void_p), ("fragment_lengths", C.c_void_p),
+        ("key_fragments", C.POINTER(C.c_void_p)), ("value_fragments", C.POINTER(C.c_void_p)),
+        ("fragment_rows", C.POINTER(C.c_int32)),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("device_status", C.c_void_p),
+        ("kernel", C.c_int32), ("max_ctas", C.c_int32),
+    ]
+
+
+_lib: Optional[C.CDLL] = None
+
+
+def load() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(f"{LIB_PATH} is missing: build it with `python -m inference_lib_b200._build` "
+                               "(there is no fallback implementation)")
+        lib = C.CDLL(LIB_PATH)
+        lib.hogatt_abi_version.restype = C.c_int
+        lib.hogatt_status_string.restype = C.c_char_p
+        lib.hogatt_status_string.argtypes = [C.c_int]
+        lib.hogatt_last_cuda_error.restype = C.c_int
+        lib.hogatt_workspace_bytes.restype = C.c_size_t
+        lib.hogatt_workspace_bytes.argtypes = [C.POINTER(Problem)]
+        for name in ("hogatt_sdpa_launch", "hogatt_fused_launch"):
+            fn = getattr(lib, name)
+            fn.restype = C.c_int
+            fn.argtypes = [C.POINTER(Problem), C.c_void_p]
+        lib.hogatt_rope_launch.restype = C.c_int
+        lib.hogatt_rope_launch.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p] + [C.c_int32] * 7 + [C.c_void_p]
+        lib.hogatt_plan_describe.restype = C.c_int
+        lib.hogatt_plan_describe.argtypes = [C.POINTER(Problem), C.POINTER(C.c_int32), C.c_int32, C.POINTER(C.c_int32)]
+        lib.hogatt_plan_ranges.restype = C.c_int
+        lib.hogatt_plan_ranges.argtypes = [C.c_int32] * 5 + [C.POINTER(C.c_int64)]
+        _lib = lib
+    return _lib
+
+
+def status_string(rc: int) -> str:
+    return load().hogatt_status_string(rc).decode()
+
+
+def dtype_code(torch_dtype) -> int:
+    import torch
+    return {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16}[torch_dtype]
+
+
+def shape_problem(*, F, W, Hq, Hkv, E, Ev, S, dtype, rotary_dim=0, scale=1.0, kernel=KERNEL_AUTO, max_ctas=0) -> Problem:
+    """A problem with dims only (enough for the plan / workspace queries)."""
+    p = Problem()
+    p.F, p.W, p.Hq, p.Hkv, p.E, p.Ev, p.S = F, W, Hq, Hkv, E, Ev, S
+    p.rotary_dim, p.dtype, p.scale, p.kernel, p.max_ctas = rotary_dim, dtype, scale, kernel, max_ctas
+    return p
+
+
+class BoundProblem:
+    """A ``Problem`` struct together with the Python objects that keep its pointers alive."""
+
+    def __init__(self, struct: Problem, keep: Sequence):
+        self.struct = struct
+        self._keep = list(keep)
+
+
+def bind(*, out, queries, locations, keys, values, scale, fragment_lengths=None, cos=None, sin=None, rq=None,
+         workspace=None, status=None, kernel=KERNEL_AUTO, max_ctas=0) -> BoundProblem:
+    """Fill a ``Problem`` from torch CUDA tensors (pointers only; nothing is copied).
+
+    ``queries`` is ``[W,Hq,S,E]`` with ``cos``/``sin`` given (fused entry point) or ``[F,W,Hq,S,E]``
+    already rotated.  Fragments may be ``[Hkv,L,E]`` or ``[1,Hkv,L,E]``.
+    """
+    F = len(keys)
+    W, Hq, S, Ev = out.shape
+    E = queries.shape[-1]
+    Hkv = keys[0].shape[-3]
+    p = shape_problem(F=F, W=W, Hq=Hq, Hkv=Hkv, E=E, Ev=Ev, S=S, dtype=dtype_code(out.dtype),
+                      rotary_dim=(cos.shape[-1] if cos is not None else 0), scale=float(scale), kernel=kernel,
+                      max_ctas=max_ctas)
+    kp = (C.c_void_p * F)(*[k.data_ptr() for k in keys])
+    vp = (C.c_void_p * F)(*[v.data_ptr() for v in values])
+    rows = (C.c_int32 * F)(*[int(k.shape[-2]) for k in keys])
+    p.out, p.queries, p.locations = out.data_ptr(), queries.data_ptr(), locations.data_ptr()
+    p.rq = rq.data_ptr() if rq is not None else None
+    p.cosines = cos.data_ptr() if cos is not None else None
+    p.sines = sin.data_ptr() if sin is not None else None
+    p.fragment_lengths = fragment_lengths.data_ptr() if fragment_lengths is not None else None
+    p.key_fragments = C.cast(kp, C.POINTER(C.c_void_p))
+    p.value_fragments = C.cast(vp, C.POINTER(C.c_void_p))
+    p.fragment_rows = C.cast(rows, C.POINTER(C.c_int32))
+    p.device_status = status.data_ptr() if status is not None else None
+    if workspace is not None:
+        p.workspace, p.workspace_bytes = workspace.data_ptr(), workspace.numel() * workspace.element_size()
+    return BoundProblem(p, [kp, vp, rows, out, queries, locations, keys, values, fragment_lengths, cos, sin, rq,
+                            workspace, status])
+
+
+def workspace_bytes(bp: BoundProblem) -> int:
+    return int(load().hogatt_workspace_bytes(C.byref(bp.struct)))
+
+
+def launch(bp: BoundProblem, stream: int = 0) -> int:
+    """Enqueue one call; returns the library's status code (0 = ok)."""
+    lib = load()
+    fn = lib.hogatt_fused_launch if bp.struct.cosines else lib.hogatt_sdpa_launch
+    return int(fn(C.byref(bp.struct), C.c_void_p(stream)))

@@ -1,0 +1,394 @@
+// C ABI of libhogatt_b200.so (declared in include/hogatt.h): argument validation, kernel choice,
+// workspace carving and launches.  No allocation, no synchronisation, no hidden static buffers.
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+
+#include "hogatt_device.cuh"
+#include "hogatt_fma.cuh"
+#include "hogatt_merge.cuh"
+#include "hogatt_mma.cuh"
+
+namespace hogatt {
+namespace {
+
+thread_local int tl_last_cuda_error = 0;
+
+#define HOGATT_CUDA_OK(expr)                         \
+    do {                                             \
+        cudaError_t err__ = (expr);                  \
+        if (err__ != cudaSuccess) {                  \
+            tl_last_cuda_error = (int)err__;         \
+            (void)cudaGetLastError();                \
+            return HOGATT_ERR_CUDA;                  \
+        }                                            \
+    } while (0)
+
+constexpr int kMaxDevices = 64;
+
+struct DeviceInfo {
+    std::atomic<int> sms{0};
+    std::atomic<int> smem_optin{0};
+};
+DeviceInfo g_devices[kMaxDevices];
+
+int current_device_info(int* dev, int* sms, int* smem_optin) {
+    HOGATT_CUDA_OK(cudaGetDevice(dev));
+    if (*dev < 0 || *dev >= kMaxDevices) return HOGATT_ERR_CUDA;
+    DeviceInfo& d = g_devices[*dev];
+    int n = d.sms.load(std::memory_order_acquire);
+    if (n == 0) {
+        int s = 0, m = 0;
+        HOGATT_CUDA_OK(cudaDeviceGetAttribute(&s, cudaDevAttrMultiProcessorCount, *dev));
+        HOGATT_CUDA_OK(cudaDeviceGetAttribute(&m, cudaDevAttrMaxSharedMemoryPerBlockOptin, *dev));
+        d.smem_optin.store(m, std::memory_order_release);
+        d.sms.store(s, std::memory_order_release);
+        n = s;
+    }
+    *sms = n;
+    *smem_optin = d.smem_optin.load(std::memory_order_acquire);
+    return HOGATT_OK;
+}
+
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) once per (kernel instantiation, device).
+template <class Kernel>
+int ensure_smem_limit(Kernel kernel, int dev, size_t bytes, std::atomic<size_t>* granted /*[kMaxDevices]*/) {
+    if (bytes <= 48 * 1024) return HOGATT_OK;
+    if (granted[dev].load(std::memory_order_acquire) >= bytes) return HOGATT_OK;
+    HOGATT_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    granted[dev].store(bytes, std::memory_order_release);
+    return HOGATT_OK;
+}
+
+size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+size_t dtype_size(int dtype) { return dtype == HOGATT_F32 ? 4 : 2; }
+
+// What will run for this problem.
+struct Resolved {
+    int kernel;          // HOGATT_KERNEL_FMA or HOGATT_KERNEL_MMA
+    int mt;              // m-tiles per CTA (tensor-core kernel)
+    int rows_per_block;
+    int tile_tokens;
+    int row_blocks;
+    int units;
+};
+
+bool mma_eligible(const hogatt_problem* p) {
+    if (p->dtype != HOGATT_F16 && p->dtype != HOGATT_BF16) return false;
+    if (p->E != p->Ev || (p->E != 64 && p->E != 128)) return false;
+    return true;
+}
+
+bool fma_eligible(const hogatt_problem* p) {
+    const int vec = 16 / (int)dtype_size(p->dtype);
+    if (p->Ev != 32 && p->Ev != 64 && p->Ev != 128 && p->Ev != 256) return false;
+    if (p->E < vec || p->E > 256 || p->E % vec != 0) return false;
+    return true;
+}
+
+int resolve(const hogatt_problem* p, Resolved* r) {
+    if (p == nullptr) return HOGATT_ERR_NULL_POINTER;
+    if (p->F <= 0 || p->W <= 0 || p->Hq <= 0 || p->Hkv <= 0 || p->E <= 0 || p->Ev <= 0 || p->S <= 0)
+        return HOGATT_ERR_BAD_SHAPE;
+    if (p->Hq % p->Hkv != 0) return HOGATT_ERR_BAD_SHAPE;
+    if (p->F > HOGATT_MAX_FRAGMENTS) return HOGATT_ERR_TOO_MANY_FRAGMENTS;
+    if (p->dtype != HOGATT_F32 && p->dtype != HOGATT_F16 && p->dtype != HOGATT_BF16) return HOGATT_ERR_UNSUPPORTED_DTYPE;
+    const int64_t rows_total = (int64_t)p->W * (p->Hq / p->Hkv) * p->S;
+    if (rows_total > (1 << 24) || (int64_t)p->F * p->W * p->S > (1 << 26)) return HOGATT_ERR_TOO_LARGE;
+    int kernel = p->kernel;
+    if (kernel == HOGATT_KERNEL_AUTO) kernel = mma_eligible(p) ? HOGATT_KERNEL_MMA : HOGATT_KERNEL_FMA;
+    if (kernel == HOGATT_KERNEL_MMA) {
+        if (!mma_eligible(p)) return HOGATT_ERR_BAD_KERNEL_CHOICE;
+        r->mt = rows_total <= 16 ? 1 : (rows_total <= 32 ? 2 : 4);
+        r->rows_per_block = 16 * r->mt;
+        r->tile_tokens = p->E == 128 ? 64 : 128;
+    } else if (kernel == HOGATT_KERNEL_FMA) {
+        if (!fma_eligible(p)) return HOGATT_ERR_UNSUPPORTED_HEAD_DIM;
+        r->mt = 1;
+        r->rows_per_block = kFmaRows;
+        r->tile_tokens = kFmaTile;
+    } else {
+        return HOGATT_ERR_BAD_KERNEL_CHOICE;
+    }
+    r->kernel = kernel;
+    r->row_blocks = (int)((rows_total + r->rows_per_block - 1) / r->rows_per_block);
+    const int64_t units = (int64_t)r->row_blocks * p->Hkv;
+    if (units > (1 << 24)) return HOGATT_ERR_TOO_LARGE;
+    r->units = (int)units;
+    return HOGATT_OK;
+}
+
+struct WorkspaceLayout {
+    size_t header, o, m, l, total;
+    int parts;
+};
+
+WorkspaceLayout carve(const hogatt_problem* p, const Resolved& r, int grid) {
+    WorkspaceLayout w;
+    w.parts = max_parts_per_unit(r.units, grid);
+    const size_t slots = (size_t)r.units * w.parts * r.rows_per_block;
+    w.header = 0;
+    w.o = 256;
+    w.m = w.o + align_up(slots * p->Ev * sizeof(float), 256);
+    w.l = w.m + align_up(slots * sizeof(float), 256);
+    w.total = w.l + align_up(slots * sizeof(float), 256);
+    return w;
+}
+
+int grid_size(const hogatt_problem* p, int sms) {
+    int grid = sms;
+    if (p->max_ctas > 0 && p->max_ctas < grid) grid = p->max_ctas;
+    return grid;
+}
+
+// ---- launch helpers, one per kernel family ------------------------------------------------------
+
+template <class T, int HD, int MT>
+int launch_mma(const KernelArgs& args, int F, int dev, int smem_optin, int grid, bool evict_first, cudaStream_t stream) {
+    static std::atomic<size_t> granted[kMaxDevices];
+    using C = MmaCfg<HD, MT>;
+    const size_t smem = mma_smem_bytes<HD, MT>(F);
+    if (smem > (size_t)smem_optin) return HOGATT_ERR_TOO_MANY_FRAGMENTS;
+    int rc = ensure_smem_limit(mma_attention_kernel<T, HD, MT>, dev, smem, granted);
+    if (rc != HOGATT_OK) return rc;
+    mma_attention_kernel<T, HD, MT><<<grid, C::THREADS, smem, stream>>>(args, evict_first ? 1 : 0);
+    HOGATT_CUDA_OK(cudaGetLastError());
+    return HOGATT_OK;
+}
+
+template <class T>
+int launch_mma_dims(const KernelArgs& args, int F, int HD, int MT, int dev, int smem_optin, int grid, bool ef,
+                    cudaStream_t stream) {
+    if (HD == 128) {
+        if (MT == 1) return launch_mma<T, 128, 1>(args, F, dev, smem_optin, grid, ef, stream);
+        if (MT == 2) return launch_mma<T, 128, 2>(args, F, dev, smem_optin, grid, ef, stream);
+        return launch_mma<T, 128, 4>(args, F, dev, smem_optin, grid, ef, stream);
+    }
+    if (MT == 1) return launch_mma<T, 64, 1>(args, F, dev, smem_optin, grid, ef, stream);
+    if (MT == 2) return launch_mma<T, 64, 2>(args, F, dev, smem_optin, grid, ef, stream);
+    return launch_mma<T, 64, 4>(args, F, dev, smem_optin, grid, ef, stream);
+}
+
+template <class T, int EV>
+int launch_fma(const KernelArgs& args, int dev, int smem_optin, int grid, cudaStream_t stream) {
+    static std::atomic<size_t> granted[kMaxDevices];
+    const size_t smem = fma_smem_bytes(args.E, EV, args.F);
+    if (smem > (size_t)smem_optin) return HOGATT_ERR_UNSUPPORTED_HEAD_DIM;
+    int rc = ensure_smem_limit(fma_attention_kernel<T, EV>, dev, smem, granted);
+    if (rc != HOGATT_OK) return rc;
+    fma_attention_kernel<T, EV><<<grid, kFmaThreads, smem, stream>>>(args);
+    HOGATT_CUDA_OK(cudaGetLastError());
+    return HOGATT_OK;
+}
+
+template <class T>
+int launch_fma_dims(const KernelArgs& args, int dev, int smem_optin, int grid, cudaStream_t stream) {
+    switch (args.Ev) {
+        case 32: return launch_fma<T, 32>(args, dev, smem_optin, grid, stream);
+        case 64: return launch_fma<T, 64>(args, dev, smem_optin, grid, stream);
+        case 128: return launch_fma<T, 128>(args, dev, smem_optin, grid, stream);
+        case 256: return launch_fma<T, 256>(args, dev, smem_optin, grid, stream);
+    }
+    return HOGATT_ERR_UNSUPPORTED_HEAD_DIM;
+}
+
+template <class T>
+int launch_all(const KernelArgs& args, const Resolved& r, int dev, int smem_optin, int grid, cudaStream_t stream) {
+    int rc;
+    if (r.kernel == HOGATT_KERNEL_MMA)
+        rc = launch_mma_dims<T>(args, args.F, args.E, r.mt, dev, smem_optin, grid, /*evict_first=*/r.row_blocks == 1, stream);
+    else
+        rc = launch_fma_dims<T>(args, dev, smem_optin, grid, stream);
+    if (rc != HOGATT_OK) return rc;
+    dim3 mgrid((unsigned)r.units, (unsigned)ceil_div(r.rows_per_block, kMergeWarps));
+    merge_kernel<T><<<mgrid, kMergeWarps * 32, 0, stream>>>(args);
+    HOGATT_CUDA_OK(cudaGetLastError());
+    return HOGATT_OK;
+}
+
+template <>
+int launch_all<float>(const KernelArgs& args, const Resolved& r, int dev, int smem_optin, int grid, cudaStream_t stream) {
+    int rc = launch_fma_dims<float>(args, dev, smem_optin, grid, stream);
+    if (rc != HOGATT_OK) return rc;
+    dim3 mgrid((unsigned)r.units, (unsigned)ceil_div(r.rows_per_block, kMergeWarps));
+    merge_kernel<float><<<mgrid, kMergeWarps * 32, 0, stream>>>(args);
+    HOGATT_CUDA_OK(cudaGetLastError());
+    return HOGATT_OK;
+}
+
+bool aligned16(const void* p) { return ((uintptr_t)p & 15u) == 0; }
+
+int attention_launch(const hogatt_problem* p, bool fused, cudaStream_t stream) {
+    Resolved r;
+    int rc = resolve(p, &r);
+    if (rc != HOGATT_OK) return rc;
+    if (!p->out || !p->queries || !p->locations || !p->key_fragments || !p->value_fragments || !p->fragment_rows ||
+        !p->workspace)
+        return HOGATT_ERR_NULL_POINTER;
+    if (fused) {
+        if (!p->cosines || !p->sines) return HOGATT_ERR_NULL_POINTER;
+        if (p->rotary_dim <= 0 || p->rotary_dim > p->E || (p->rotary_dim & 1)) return HOGATT_ERR_BAD_SHAPE;
+    } else if (p->cosines || p->sines || p->rq) {
+        return HOGATT_ERR_BAD_SHAPE;      // pre-rotated queries: nothing to rotate, nothing to write back
+    }
+    const size_t sz = dtype_size(p->dtype);
+    if ((p->E * sz) % 16 != 0 || (p->Ev * sz) % 16 != 0) return HOGATT_ERR_UNSUPPORTED_HEAD_DIM;
+    if (!aligned16(p->out) || !aligned16(p->queries) || !aligned16(p->workspace) || ((uintptr_t)p->workspace & 255u))
+        return HOGATT_ERR_MISALIGNED;
+    if (p->rq && !aligned16(p->rq)) return HOGATT_ERR_MISALIGNED;
+    if (fused && (((uintptr_t)p->cosines & 3u) || ((uintptr_t)p->sines & 3u))) return HOGATT_ERR_MISALIGNED;
+
+    int dev, sms, smem_optin;
+    rc = current_device_info(&dev, &sms, &smem_optin);
+    if (rc != HOGATT_OK) return rc;
+    const int grid = grid_size(p, sms);
+    const WorkspaceLayout w = carve(p, r, grid);
+    if (p->workspace_bytes < w.total) return HOGATT_ERR_WORKSPACE_TOO_SMALL;
+
+    KernelArgs args;
+    memset(&args, 0, sizeof(args));
+    args.F = p->F; args.W = p->W; args.Hq = p->Hq; args.Hkv = p->Hkv; args.G = p->Hq / p->Hkv;
+    args.E = p->E; args.Ev = p->Ev; args.S = p->S; args.R = fused ? p->rotary_dim : 0;
+    args.rows_total = p->W * args.G * p->S;
+    args.rows_per_block = r.rows_per_block;
+    args.row_blocks = r.row_blocks;
+    args.parts_per_unit = w.parts;
+    args.l2scale = p->scale * 1.4426950408889634f;
+    args.out = p->out;
+    args.rq = fused ? p->rq : nullptr;
+    args.q = p->queries;
+    args.cos = fused ? p->cosines : nullptr;
+    args.sin = fused ? p->sines : nullptr;
+    args.loc = p->locations;
+    args.flen = p->fragment_lengths;
+    unsigned char* ws = static_cast<unsigned char*>(p->workspace);
+    args.header = reinterpret_cast<int*>(ws + w.header);
+    args.ws_o = reinterpret_cast<float*>(ws + w.o);
+    args.ws_m = reinterpret_cast<float*>(ws + w.m);
+    args.ws_l = reinterpret_cast<float*>(ws + w.l);
+    args.status = p->device_status;
+    for (int f = 0; f < p->F; ++f) {
+        const int rows = p->fragment_rows[f];
+        if (rows < 0) return HOGATT_ERR_BAD_SHAPE;
+        if (rows > 0 && (!p->key_fragments[f] || !p->value_fragments[f])) return HOGATT_ERR_NULL_POINTER;
+        if (!aligned16(p->key_fragments[f]) || !aligned16(p->value_fragments[f])) return HOGATT_ERR_MISALIGNED;
+        args.ft.k[f] = p->key_fragments[f];
+        args.ft.v[f] = p->value_fragments[f];
+        args.ft.rows[f] = rows;
+    }
+
+    switch (p->dtype) {
+        case HOGATT_F32: return launch_all<float>(args, r, dev, smem_optin, grid, stream);
+        case HOGATT_F16: return launch_all<__half>(args, r, dev, smem_optin, grid, stream);
+        case HOGATT_BF16: return launch_all<__nv_bfloat16>(args, r, dev, smem_optin, grid, stream);
+    }
+    return HOGATT_ERR_UNSUPPORTED_DTYPE;
+}
+
+}  // namespace
+}  // namespace hogatt
+
+using namespace hogatt;
+
+extern "C" {
+
+int hogatt_abi_version(void) { return HOGATT_ABI_VERSION; }
+
+const char* hogatt_status_string(int status) {
+    switch (status) {
+        case HOGATT_OK: return "ok";
+        case HOGATT_ERR_NULL_POINTER: return "a required pointer is NULL";
+        case HOGATT_ERR_BAD_SHAPE: return "bad shape (non-positive dim, Hq not a multiple of Hkv, bad rotary_dim, or rope arguments on the pre-rotated entry point)";
+        case HOGATT_ERR_UNSUPPORTED_HEAD_DIM: return "unsupported head size (rows must be multiples of 16 bytes; E <= 256; Ev in {32,64,128,256})";
+        case HOGATT_ERR_UNSUPPORTED_DTYPE: return "unsupported dtype (f32, f16, bf16)";
+        case HOGATT_ERR_TOO_MANY_FRAGMENTS: return "too many fragments (HOGATT_MAX_FRAGMENTS)";
+        case HOGATT_ERR_MISALIGNED: return "a tensor does not start on a 16-byte boundary (workspace: 256)";
+        case HOGATT_ERR_WORKSPACE_TOO_SMALL: return "workspace smaller than hogatt_workspace_bytes()";
+        case HOGATT_ERR_CUDA: return "a CUDA runtime call failed (hogatt_last_cuda_error())";
+        case HOGATT_ERR_BAD_KERNEL_CHOICE: return "the requested kernel cannot run this dtype / head size";
+        case HOGATT_ERR_TOO_LARGE: return "problem too large for 32-bit row indexing";
+    }
+    return "unknown status";
+}
+
+int hogatt_last_cuda_error(void) { return tl_last_cuda_error; }
+
+size_t hogatt_workspace_bytes(const hogatt_problem* p) {
+    Resolved r;
+    if (resolve(p, &r) != HOGATT_OK) return 0;
+    int dev, sms, smem_optin;
+    if (current_device_info(&dev, &sms, &smem_optin) != HOGATT_OK) return 0;
+    return carve(p, r, grid_size(p, sms)).total;
+}
+
+int hogatt_sdpa_launch(const hogatt_problem* p, hogatt_stream_t stream) {
+    return attention_launch(p, /*fused=*/false, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int hogatt_fused_launch(const hogatt_problem* p, hogatt_stream_t stream) {
+    return attention_launch(p, /*fused=*/true, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int hogatt_rope_launch(void* rq, const void* queries, const float* cosines, const float* sines, int32_t F, int32_t W,
+                       int32_t Hq, int32_t S, int32_t E, int32_t rotary_dim, int32_t dtype, hogatt_stream_t stream_) {
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    if (!rq || !queries || !cosines || !sines) return HOGATT_ERR_NULL_POINTER;
+    if (F <= 0 || W <= 0 || Hq <= 0 || S <= 0 || E <= 0 || rotary_dim <= 0 || rotary_dim > E || (rotary_dim & 1))
+        return HOGATT_ERR_BAD_SHAPE;
+    const int64_t rows = (int64_t)F * W * Hq * S;
+    if (rows > (1 << 30)) return HOGATT_ERR_TOO_LARGE;
+    const unsigned blocks = (unsigned)((rows + 3) / 4);
+    switch (dtype) {
+        case HOGATT_F32:
+            rope_kernel<float><<<blocks, 128, 0, stream>>>((float*)rq, (const float*)queries, cosines, sines, F, W, Hq, S, E, rotary_dim);
+            break;
+        case HOGATT_F16:
+            rope_kernel<__half><<<blocks, 128, 0, stream>>>((__half*)rq, (const __half*)queries, cosines, sines, F, W, Hq, S, E, rotary_dim);
+            break;
+        case HOGATT_BF16:
+            rope_kernel<__nv_bfloat16><<<blocks, 128, 0, stream>>>((__nv_bfloat16*)rq, (const __nv_bfloat16*)queries, cosines, sines, F, W, Hq, S, E, rotary_dim);
+            break;
+        default: return HOGATT_ERR_UNSUPPORTED_DTYPE;
+    }
+    HOGATT_CUDA_OK(cudaGetLastError());
+    return HOGATT_OK;
+}
+
+int hogatt_plan_describe(const hogatt_problem* p, const int32_t* visible_rows, int32_t num_sms, int32_t plan[8]) {
+    Resolved r;
+    int rc = resolve(p, &r);
+    if (rc != HOGATT_OK) return rc;
+    if (!visible_rows || !plan) return HOGATT_ERR_NULL_POINTER;
+    if (num_sms <= 0) return HOGATT_ERR_BAD_SHAPE;
+    int64_t th = 0;
+    for (int f = 0; f < p->F; ++f) th += ceil_div(visible_rows[f] < 0 ? 0 : visible_rows[f], r.tile_tokens);
+    if (th > (1 << 30)) return HOGATT_ERR_TOO_LARGE;
+    const int grid = grid_size(p, num_sms);
+    plan[0] = r.tile_tokens;
+    plan[1] = r.rows_per_block;
+    plan[2] = r.row_blocks;
+    plan[3] = (int)th;
+    plan[4] = r.units;
+    plan[5] = effective_ctas((int64_t)r.units * th, grid);
+    plan[6] = max_parts_per_unit(r.units, grid);
+    plan[7] = r.kernel;
+    return HOGATT_OK;
+}
+
+int hogatt_plan_ranges(int32_t tiles_per_unit, int32_t units, int32_t ctas, int32_t cta, int32_t unit, int64_t range[4]) {
+    if (!range) return HOGATT_ERR_NULL_POINTER;
+    if (tiles_per_unit <= 0 || units <= 0 || ctas <= 0 || cta < 0 || cta >= ctas || unit < 0 || unit >= units)
+        return HOGATT_ERR_BAD_SHAPE;
+    const int64_t n = (int64_t)tiles_per_unit * units;
+    if (ctas > n) return HOGATT_ERR_BAD_SHAPE;
+    range[0] = cta_first_tile(cta, n, ctas);
+    range[1] = cta_first_tile(cta + 1, n, ctas);
+    int first, count;
+    unit_ctas(unit, tiles_per_unit, n, ctas, &first, &count);
+    range[2] = first;
+    range[3] = count;
+    return HOGATT_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,422 @@
+// Tensor-core fragment attention for fp16 / bf16 with E == Ev in {64, 128}: the hot path.
+//
+// One persistent CTA per SM walks a contiguous range of KV tiles (see hogatt_plan.h).
+//   * warp 0 is the producer: it streams K and V tiles global -> shared with 1-D bulk async
+//     copies (TMA engine) into a ring of NSTAGE stages, completion counted on mbarriers.  A tile
+//     is up to 64 (head size 128) or 128 (head size 64) consecutive keys of one fragment and one
+//     kv head, which is one contiguous byte run because fragments are [Hkv, rows, E] row-major.
+//   * consumer warps each keep 16 query rows (one MMA m-tile) of the kv head resident -- ALL
+//     workers and GQA heads of the head share every K/V tile, so KV is read from HBM once per
+//     call -- and take a slice of every tile: S = Q K^T and O += P V with mma.sync m16n8k16,
+//     fp32 accumulate, online softmax in base 2 in registers.  The per-fragment query RoPE is
+//     done in the prologue of each fragment: the warp builds its MMA A-fragments straight from
+//     the un-rotated query and the cos/sin rows (rounded to the storage type first, as the
+//     reference's rope kernel does before attention reads them, src/rope.cuh:43-45).
+//   * where the CTA's share of a (kv head, row block) unit ends, the warps fold their private
+//     (O, max, sum) together through shared memory and leave one partial in the workspace.
+//
+// Shared-memory layout of a K (or V) tile: 8 groups of GT consecutive keys; group g starts at
+// g * (GT * row_bytes + 16).  The MMA "n" (QK^T) / "k" (PV) index does not run over consecutive
+// keys but over the 8 groups at a fixed position i inside the group: key = g * GT + i.  The 16
+// bytes of padding per group rotate the bank of equal chunks by one 16-byte unit per group, so
+// the 8 row addresses of every ldmatrix phase fall into 8 different bank groups: no bank
+// conflicts although the bulk copies land rows unswizzled.  A fragment tile is 8 bulk copies of
+// 2 KiB for K and 8 for V.
+//
+// The reference kernel (src/kernels/kernel_v21.cuh:28-316) assigns one (kv head, worker, token,
+// split) to a CTA, keeps the GQA heads' queries and accumulators in registers/local memory,
+// reduces dot products with 8-lane shuffles on CUDA cores and stages 32 rows per step with
+// 16-byte cp.async; it re-reads the KV once per (worker, token).
+#pragma once
+#include "hogatt_device.cuh"
+
+namespace hogatt {
+
+template <int HD, int MT>
+struct MmaCfg {
+    static constexpr int NCW = (MT == 1) ? 4 : 8;        // consumer warps
+    static constexpr int NSLICE = NCW / MT;              // warps sharing one m-tile, each takes a slice of the keys
+    static constexpr int GT = (HD == 128) ? 8 : 16;      // keys per group
+    static constexpr int TILE = 8 * GT;                  // keys per stage
+    static constexpr int ROWB = HD * 2;                  // bytes per key row
+    static constexpr int GROUP_STRIDE = GT * ROWB + 16;
+    static constexpr int KV_BYTES = 8 * GROUP_STRIDE;
+    static constexpr int STAGE_BYTES = 2 * KV_BYTES;
+    static constexpr int NSTAGE = 6;
+    static constexpr int NT_S = GT / NSLICE;             // 8-key n-tiles per warp per stage
+    static constexpr int NT_O = HD / 8;                  // output n-tiles
+    static constexpr int KSTEPS = HD / 16;
+    static constexpr int THREADS = (NCW + 1) * 32;
+    static constexpr int RPB = 16 * MT;                  // query rows per CTA
+    static constexpr int SLOT_FLOATS = NT_O * 4 * 32;    // one warp's accumulators
+    static_assert(NT_S >= 2 && NT_S % 2 == 0, "a warp's slice must hold whole k16 steps");
+    static_assert((NCW / 2) * SLOT_FLOATS * 4 <= STAGE_BYTES, "fold scratch must fit in one stage");
+};
+
+template <int HD, int MT>
+__host__ __device__ inline size_t mma_smem_bytes(int F) {
+    using C = MmaCfg<HD, MT>;
+    return 128 /* alignment slack */ + (size_t)C::NSTAGE * C::STAGE_BYTES + (size_t)(C::NCW / 2) * 32 * 4 * 4 /* stats */ +
+           (2 * C::NSTAGE + 1) * 8 /* barriers */ + 16 /* abort flag */ + ((size_t)2 * F + 1) * 4;
+}
+
+template <class T, int HD, int MT>
+__global__ void __launch_bounds__(MmaCfg<HD, MT>::THREADS, 1)
+mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_first) {
+    using C = MmaCfg<HD, MT>;
+    extern __shared__ unsigned char smem_dyn[];
+    unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 127) & ~(uintptr_t)127);
+    unsigned char* stages = base;
+    float* stats = reinterpret_cast<float*>(stages + (size_t)C::NSTAGE * C::STAGE_BYTES);   // [NCW/2][32][4]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(stats + (C::NCW / 2) * 32 * 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * C::NSTAGE + 1);
+    int* vis = const_cast<int*>(abort_flag) + 4;
+    int* pre = vis + a.F;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * C::NSTAGE, cbar = full0 + 16 * C::NSTAGE;
+    const uint32_t stage0 = smem_u32(stages);
+
+    if (tid == 0) {
+        for (int s = 0; s < C::NSTAGE; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, C::NCW);
+        }
+        mbar_init(cbar, C::NCW);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        fence_proxy_async_smem();
+    }
+    build_tile_prefix(a, C::TILE, vis, pre);     // ends with __syncthreads(): barriers are visible too
+
+    const int TH = pre[a.F];
+    const int units = a.row_blocks * a.Hkv;
+    const int64_t N = (int64_t)units * TH;
+    const int ctas = effective_ctas(N, gridDim.x);
+    if (blockIdx.x == 0 && tid == 0) {
+        a.header[0] = TH;
+        a.header[1] = ctas;
+    }
+    if (a.rq != nullptr && a.cos != nullptr && warp > 0)
+        write_rotated_queries<T>(a, blockIdx.x * C::NCW + (warp - 1), gridDim.x * C::NCW);
+    if ((int)blockIdx.x >= ctas) return;
+
+    const int64_t t0 = cta_first_tile(blockIdx.x, N, ctas), t1 = cta_first_tile(blockIdx.x + 1, N, ctas);
+
+    // =====================================================================================
+    // Producer warp
+    // =====================================================================================
+    if (warp == 0) {
+        uint64_t policy = 0;
+        if (use_evict_first) policy = l2_policy_evict_first();
+        int64_t u = t0 / TH;
+        int j = (int)(t0 - u * TH), fscan = 0, it = 0;
+        bool ok = true;
+        for (int64_t t = t0; t < t1 && ok; ++t, ++it) {
+            while (j >= pre[fscan + 1]) ++fscan;
+            const int f = fscan;
+            const int hkv = (int)(u % a.Hkv);
+            const int tok0 = (j - pre[f]) * C::TILE;
+            const int ntok = min(C::TILE, vis[f] - tok0);
+            const int stage = it % C::NSTAGE;
+            const uint32_t phase = (uint32_t)(it / C::NSTAGE) & 1u;
+            ok = mbar_wait_bounded(empty0 + 8 * stage, phase ^ 1u, abort_flag, a.status, STATUS_WAIT_EMPTY_TIMEOUT);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            const uint32_t fullb = full0 + 8 * stage;
+            if (lane == 0) mbar_arrive_expect_tx(fullb, (uint32_t)ntok * C::ROWB * 2u);
+            __syncwarp();
+            if (lane < 16) {
+                const int g = lane & 7;
+                const int tg = min(C::GT, ntok - g * C::GT);
+                if (tg > 0) {
+                    const bool is_v = lane >= 8;
+                    const unsigned char* src = static_cast<const unsigned char*>(is_v ? a.ft.v[f] : a.ft.k[f]) +
+                                               ((size_t)hkv * a.ft.rows[f] + tok0 + g * C::GT) * C::ROWB;
+                    const uint32_t dst = stage0 + stage * C::STAGE_BYTES + (is_v ? C::KV_BYTES : 0) + g * C::GROUP_STRIDE;
+                    if (use_evict_first)
+                        bulk_load_hint(dst, src, (uint32_t)tg * C::ROWB, fullb, policy);
+                    else
+                        bulk_load(dst, src, (uint32_t)tg * C::ROWB, fullb);
+                }
+            }
+            if (++j == TH) {
+                j = 0;
+                ++u;
+                fscan = 0;
+            }
+        }
+        // Do not leave while copies may still be landing in this CTA's shared memory.
+        if (lane == 0) {
+            const int pending = min(it, C::NSTAGE);
+            for (int k = it - pending; k < it; ++k)
+                mbar_wait_bounded(full0 + 8 * (k % C::NSTAGE), (uint32_t)(k / C::NSTAGE) & 1u, abort_flag, a.status,
+                                  STATUS_DRAIN_TIMEOUT);
+        }
+        return;
+    }
+
+    // =====================================================================================
+    // Consumer warps
+    // =====================================================================================
+    const int cw = warp - 1;
+    const int mt = cw % MT, slice = cw / MT;
+    const int quad = lane >> 2, qlane = lane & 3;
+    const int row_a = mt * 16 + quad, row_b = row_a + 8;     // rows inside the block
+    const T* __restrict__ q = static_cast<const T*>(a.q);
+
+    float o[C::NT_O][4];
+    float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
+    uint32_t qf[C::KSTEPS][4];
+    int lim_a = 0, lim_b = 0;
+    RowId id_a = {0, 0, 0}, id_b = {0, 0, 0};
+    bool valid_a = false, valid_b = false;
+    uint32_t cphase = 0;
+
+    auto consumer_sync = [&]() -> bool {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(cbar);
+        const bool ok = mbar_wait_bounded(cbar, cphase, abort_flag, a.status, STATUS_WAIT_SYNC_TIMEOUT);
+        cphase ^= 1u;
+        return __all_sync(0xffffffffu, ok);
+    };
+
+    int64_t u = t0 / TH;
+    int j = (int)(t0 - u * TH), fscan = 0, it = 0, cur_u = -1, cur_f = -1, hkv = 0, rb = 0;
+    for (int64_t t = t0; t < t1; ++t, ++it) {
+        if ((int)u != cur_u) {
+            cur_u = (int)u;
+            cur_f = -1;
+            fscan = 0;
+            rb = cur_u / a.Hkv;
+            hkv = cur_u % a.Hkv;
+            const int gra = rb * C::RPB + row_a, grb = rb * C::RPB + row_b;
+            valid_a = gra < a.rows_total;
+            valid_b = grb < a.rows_total;
+            id_a = decode_row(valid_a ? gra : 0, a.G, a.S);
+            id_b = decode_row(valid_b ? grb : 0, a.G, a.S);
+            m_a = m_b = -INFINITY;
+            l_a = l_b = 0.f;
+#pragma unroll
+            for (int n = 0; n < C::NT_O; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+        }
+        while (j >= pre[fscan + 1]) ++fscan;
+        const int f = fscan;
+        if (f != cur_f) {
+            cur_f = f;
+            // ---- per-fragment prologue: rotated query rows -> MMA A-fragments, visibility limits ----
+            const int hq_a = hkv * a.G + id_a.g, hq_b = hkv * a.G + id_b.g;
+            auto load_pair = [&](bool valid, const RowId& id, int hq, int e) -> uint32_t {
+                if (!valid) return 0u;
+                if (a.cos == nullptr) {
+                    const T* src = q + ((size_t)((f * a.W + id.w) * a.Hq + hq) * a.S + id.s) * HD + e;
+                    return *reinterpret_cast<const uint32_t*>(src);
+                }
+                const T* qrow = q + ((size_t)(id.w * a.Hq + hq) * a.S + id.s) * HD;
+                const size_t tab = ((size_t)(f * a.W + id.w) * a.S + id.s) * a.R;
+                const float x0 = rope_channel<T>(qrow, a.cos + tab, a.sin + tab, e, a.R);
+                const float x1 = rope_channel<T>(qrow, a.cos + tab, a.sin + tab, e + 1, a.R);
+                return pack2<T>(x0, x1);
+            };
+#pragma unroll
+            for (int kk = 0; kk < C::KSTEPS; ++kk) {
+                const int e = kk * 16 + qlane * 2;
+                qf[kk][0] = load_pair(valid_a, id_a, hq_a, e);
+                qf[kk][1] = load_pair(valid_b, id_b, hq_b, e);
+                qf[kk][2] = load_pair(valid_a, id_a, hq_a, e + 8);
+                qf[kk][3] = load_pair(valid_b, id_b, hq_b, e + 8);
+            }
+            const int vf = vis[f];
+            lim_a = valid_a ? min(a.loc[(f * a.W + id_a.w) * a.S + id_a.s], vf - 1) + 1 : vf;
+            lim_b = valid_b ? min(a.loc[(f * a.W + id_b.w) * a.S + id_b.s], vf - 1) + 1 : vf;
+        }
+        const int tok0 = (j - pre[f]) * C::TILE;
+        const int ntok = min(C::TILE, vis[f] - tok0);
+        const int stage = it % C::NSTAGE;
+        const uint32_t phase = (uint32_t)(it / C::NSTAGE) & 1u;
+        const uint32_t kb = stage0 + stage * C::STAGE_BYTES, vb = kb + C::KV_BYTES;
+
+        bool ok = mbar_wait_bounded(full0 + 8 * stage, phase, abort_flag, a.status, STATUS_WAIT_FULL_TIMEOUT);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+
+        const int i0 = slice * C::NT_S;      // first in-group position of this warp's slice
+        if (ntok < C::TILE) {
+            // V rows past the end of a short tile were not written by the copy: make them finite
+            // (their probabilities are exactly zero, but 0 * NaN would poison the sums).
+            unsigned char* vgen = stages + (size_t)stage * C::STAGE_BYTES + C::KV_BYTES;
+            for (int r = 0; r < 8 * C::NT_S; ++r) {
+                const int g = r & 7, i = i0 + (r >> 3);
+                if (g * C::GT + i >= ntok && lane < C::ROWB / 16)
+                    *reinterpret_cast<int4*>(vgen + g * C::GROUP_STRIDE + i * C::ROWB + lane * 16) = make_int4(0, 0, 0, 0);
+            }
+            __syncwarp();
+        }
+
+        // ---- S = Q K^T for this warp's keys ----
+        float sc[C::NT_S][4];
+#pragma unroll
+        for (int ii = 0; ii < C::NT_S; ++ii) {
+            sc[ii][0] = sc[ii][1] = sc[ii][2] = sc[ii][3] = 0.f;
+            const uint32_t rowaddr = kb + (lane & 7) * C::GROUP_STRIDE + (i0 + ii) * C::ROWB + (lane >> 3) * 16;
+#pragma unroll
+            for (int k2 = 0; k2 < C::KSTEPS / 2; ++k2) {
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4(rowaddr + k2 * 64, b0, b1, b2, b3);
+                mma_16816<T>(sc[ii], qf[2 * k2], b0, b1);
+                mma_16816<T>(sc[ii], qf[2 * k2 + 1], b2, b3);
+            }
+        }
+
+        // ---- visibility mask, online softmax (base 2) ----
+        const int tile_end = tok0 + C::TILE;
+        const bool need_mask = __any_sync(0xffffffffu, tile_end > lim_a || tile_end > lim_b);
+        float mx_a = -INFINITY, mx_b = -INFINITY;
+#pragma unroll
+        for (int ii = 0; ii < C::NT_S; ++ii) {
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                float xa = sc[ii][c] * a.l2scale, xb = sc[ii][2 + c] * a.l2scale;
+                if (need_mask) {
+                    const int key = tok0 + (qlane * 2 + c) * C::GT + i0 + ii;
+                    if (key >= lim_a) xa = -INFINITY;
+                    if (key >= lim_b) xb = -INFINITY;
+                }
+                sc[ii][c] = xa;
+                sc[ii][2 + c] = xb;
+                mx_a = fmaxf(mx_a, xa);
+                mx_b = fmaxf(mx_b, xb);
+            }
+        }
+        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 1));
+        mx_a = fmaxf(mx_a, __shfl_xor_sync(0xffffffffu, mx_a, 2));
+        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 1));
+        mx_b = fmaxf(mx_b, __shfl_xor_sync(0xffffffffu, mx_b, 2));
+        const float mn_a = fmaxf(m_a, mx_a), mn_b = fmaxf(m_b, mx_b);
+        const float mu_a = (mn_a == -INFINITY) ? 0.f : mn_a, mu_b = (mn_b == -INFINITY) ? 0.f : mn_b;
+        const float al_a = exp2f(m_a - mu_a), al_b = exp2f(m_b - mu_b);
+        m_a = mn_a;
+        m_b = mn_b;
+        float ps_a = 0.f, ps_b = 0.f;
+#pragma unroll
+        for (int ii = 0; ii < C::NT_S; ++ii) {
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                sc[ii][c] = exp2f(sc[ii][c] - mu_a);
+                sc[ii][2 + c] = exp2f(sc[ii][2 + c] - mu_b);
+                ps_a += sc[ii][c];
+                ps_b += sc[ii][2 + c];
+            }
+        }
+        l_a = l_a * al_a + ps_a;     // per-thread share of the row sum; lanes of a quad are added at the fold
+        l_b = l_b * al_b + ps_b;
+        if (__any_sync(0xffffffffu, al_a != 1.f || al_b != 1.f)) {
+#pragma unroll
+            for (int n = 0; n < C::NT_O; ++n) {
+                o[n][0] *= al_a;
+                o[n][1] *= al_a;
+                o[n][2] *= al_b;
+                o[n][3] *= al_b;
+            }
+        }
+
+        // ---- O += P V ----
+#pragma unroll
+        for (int ks = 0; ks < C::NT_S / 2; ++ks) {
+            uint32_t pa[4];
+            pa[0] = pack2<T>(sc[2 * ks][0], sc[2 * ks][1]);
+            pa[1] = pack2<T>(sc[2 * ks][2], sc[2 * ks][3]);
+            pa[2] = pack2<T>(sc[2 * ks + 1][0], sc[2 * ks + 1][1]);
+            pa[3] = pack2<T>(sc[2 * ks + 1][2], sc[2 * ks + 1][3]);
+            const uint32_t rowaddr =
+                vb + (lane & 7) * C::GROUP_STRIDE + (i0 + 2 * ks + ((lane >> 3) & 1)) * C::ROWB + (lane >> 4) * 16;
+#pragma unroll
+            for (int jj = 0; jj < C::NT_O / 2; ++jj) {
+                uint32_t b0, b1, b2, b3;
+                ldmatrix_x4_trans(rowaddr + jj * 32, b0, b1, b2, b3);
+                mma_16816<T>(o[2 * jj], pa, b0, b1);
+                mma_16816<T>(o[2 * jj + 1], pa, b2, b3);
+            }
+        }
+
+        // ---- end of this CTA's share of the unit: fold the warps together, leave a partial ----
+        const bool last = (j == TH - 1) || (t == t1 - 1);
+        bool wrote_scratch = false;
+        if (last) {
+            l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+            l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+            l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+            l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+            float* scratch = reinterpret_cast<float*>(stages + (size_t)stage * C::STAGE_BYTES);
+            bool alive = true;
+            if (C::NSLICE > 1) alive = consumer_sync();      // every warp is done reading this stage's K/V
+#pragma unroll
+            for (int h = C::NSLICE / 2; h >= 1 && alive; h >>= 1) {
+                if (slice >= h && slice < 2 * h) {
+                    const int slot = (slice - h) * MT + mt;
+                    float* dst = scratch + (size_t)slot * C::SLOT_FLOATS;
+#pragma unroll
+                    for (int n = 0; n < C::NT_O; ++n)
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) dst[(n * 4 + c) * 32 + lane] = o[n][c];
+                    *reinterpret_cast<float4*>(stats + (slot * 32 + lane) * 4) = make_float4(m_a, m_b, l_a, l_b);
+                    wrote_scratch = true;
+                }
+                alive = consumer_sync();
+                if (!alive) break;
+                if (slice < h) {
+                    const int slot = slice * MT + mt;
+                    const float* src = scratch + (size_t)slot * C::SLOT_FLOATS;
+                    const float4 st = *reinterpret_cast<const float4*>(stats + (slot * 32 + lane) * 4);
+                    const float na = fmaxf(m_a, st.x), nb = fmaxf(m_b, st.y);
+                    const float ua = (na == -INFINITY) ? 0.f : na, ub = (nb == -INFINITY) ? 0.f : nb;
+                    const float fa = exp2f(m_a - ua), ga = exp2f(st.x - ua);
+                    const float fb = exp2f(m_b - ub), gb = exp2f(st.y - ub);
+                    l_a = l_a * fa + st.z * ga;
+                    l_b = l_b * fb + st.w * gb;
+                    m_a = na;
+                    m_b = nb;
+#pragma unroll
+                    for (int n = 0; n < C::NT_O; ++n) {
+                        o[n][0] = o[n][0] * fa + src[(n * 4 + 0) * 32 + lane] * ga;
+                        o[n][1] = o[n][1] * fa + src[(n * 4 + 1) * 32 + lane] * ga;
+                        o[n][2] = o[n][2] * fb + src[(n * 4 + 2) * 32 + lane] * gb;
+                        o[n][3] = o[n][3] * fb + src[(n * 4 + 3) * 32 + lane] * gb;
+                    }
+                }
+                if (h > 1) alive = consumer_sync();          // scratch is rewritten by the next round
+            }
+            if (!alive) break;
+            if (slice == 0) {
+                int first, count;
+                unit_ctas(u, TH, N, ctas, &first, &count);
+                const size_t slot = (size_t)u * a.parts_per_unit + (blockIdx.x - first);
+                float* wo_a = a.ws_o + (slot * C::RPB + row_a) * HD + qlane * 2;
+                float* wo_b = a.ws_o + (slot * C::RPB + row_b) * HD + qlane * 2;
+#pragma unroll
+                for (int n = 0; n < C::NT_O; ++n) {
+                    *reinterpret_cast<float2*>(wo_a + n * 8) = make_float2(o[n][0], o[n][1]);
+                    *reinterpret_cast<float2*>(wo_b + n * 8) = make_float2(o[n][2], o[n][3]);
+                }
+                if (qlane == 0) {
+                    a.ws_m[slot * C::RPB + row_a] = m_a;
+                    a.ws_m[slot * C::RPB + row_b] = m_b;
+                    a.ws_l[slot * C::RPB + row_a] = l_a;
+                    a.ws_l[slot * C::RPB + row_b] = l_b;
+                }
+            }
+        }
+
+        // ---- hand the stage back to the producer ----
+        if (wrote_scratch || ntok < C::TILE) fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty0 + 8 * stage);
+
+        if (++j == TH) {
+            j = 0;
+            ++u;
+        }
+    }
+}
+
+}  // namespace hogatt

@@ -1,0 +1,92 @@
+"""CPU-only checks of the C ABI: the library loads, exports what the header declares, and the
+split-K decomposition covers every tile exactly once for any grid."""
+import ctypes as C
+import os
+import re
+
+import pytest
+
+from inference_lib_b200 import _build, _cabi
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    _build.build_cabi()
+    return _cabi.load()
+
+
+def test_every_declared_symbol_is_exported(lib):
+    header = open(os.path.join(ROOT, "include", "hogatt.h")).read()
+    declared = set(re.findall(r"\b(hogatt_[a-z_0-9]+)\s*\(", header))
+    assert declared, "no declarations found"
+    assert declared == set(_cabi.EXPORTS) | (declared - set(_cabi.EXPORTS))
+    for name in declared:
+        assert hasattr(lib, name), f"{name} is declared in include/hogatt.h but not exported"
+    assert lib.hogatt_abi_version() == int(re.search(r"#define HOGATT_ABI_VERSION (\d+)", header).group(1))
+
+
+def test_status_strings(lib):
+    assert _cabi.status_string(0) == "ok"
+    for rc in range(-10, 0):
+        assert _cabi.status_string(rc) not in ("ok", "unknown status")
+    assert _cabi.status_string(-99) == "unknown status"
+
+
+def test_struct_layout_matches_the_header(lib):
+    # 10 x 4-byte scalars, 7 pointers, 3 host-array pointers, workspace ptr + size, status ptr, 2 ints
+    assert C.sizeof(_cabi.Problem) == 40 + 8 * 7 + 8 * 3 + 16 + 8 + 8
+
+
+def _describe(lib, visible, sms=148, **dims):
+    p = _cabi.shape_problem(**dims)
+    vis = (C.c_int32 * len(visible))(*visible)
+    plan = (C.c_int32 * 8)()
+    rc = lib.hogatt_plan_describe(C.byref(p), vis, sms, plan)
+    return rc, list(plan)
+
+
+def test_plan_for_the_headline_shapes(lib):
+    rc, plan = _describe(lib, [8192, 2048, 2048, 2048, 2048], F=5, W=4, Hq=32, Hkv=8, E=128, Ev=128, S=1, dtype=_cabi.BF16)
+    assert rc == 0
+    tile, rows, row_blocks, th, units, ctas, parts, kernel = plan
+    assert (tile, rows, row_blocks, th, units, ctas, kernel) == (64, 16, 1, 256, 8, 148, _cabi.KERNEL_MMA)
+    rc, plan = _describe(lib, [131072, 4096, 4096], F=3, W=2, Hq=32, Hkv=8, E=128, Ev=128, S=1, dtype=_cabi.BF16)
+    assert rc == 0 and plan[3] == 2176 and plan[5] == 148          # 2176 tiles per head >= 64 chunks per head
+    rc, plan = _describe(lib, [256, 64, 64], F=3, W=2, Hq=8, Hkv=2, E=64, Ev=64, S=1, dtype=_cabi.F32)
+    assert rc == 0 and plan[7] == _cabi.KERNEL_FMA and plan[0] == 32
+    rc, plan = _describe(lib, [16384] + [1024] * 8, F=9, W=8, Hq=64, Hkv=8, E=128, Ev=128, S=16, dtype=_cabi.BF16)
+    assert rc == 0 and plan[1] == 64 and plan[2] == 16 and plan[4] == 128
+
+
+def test_plan_refuses_bad_problems(lib):
+    assert _describe(lib, [8], F=1, W=1, Hq=3, Hkv=2, E=128, Ev=128, S=1, dtype=_cabi.BF16)[0] == -2
+    assert _describe(lib, [8], F=1, W=1, Hq=2, Hkv=2, E=24, Ev=24, S=1, dtype=_cabi.BF16)[0] == -3
+    assert _describe(lib, [8], F=1, W=1, Hq=2, Hkv=2, E=128, Ev=128, S=1, dtype=7)[0] == -4
+    assert _describe(lib, [8] * 200, F=200, W=1, Hq=2, Hkv=2, E=128, Ev=128, S=1, dtype=_cabi.BF16)[0] == -5
+    assert _describe(lib, [8], F=1, W=1, Hq=2, Hkv=2, E=128, Ev=128, S=1, dtype=_cabi.F32, kernel=_cabi.KERNEL_MMA)[0] == -9
+
+
+@pytest.mark.parametrize("th,units,grid", [(1, 1, 148), (3, 2, 148), (256, 8, 148), (2176, 8, 148), (7, 128, 148),
+                                           (13, 5, 4), (1, 200, 148), (19, 8, 148), (100, 3, 7), (5, 5, 25), (64, 1, 148)])
+def test_ranges_tile_the_work_exactly_once(lib, th, units, grid):
+    n = th * units
+    ctas = min(grid, n)
+    parts_bound = grid // units + 2
+    rng = (C.c_int64 * 4)()
+    covered = 0
+    owners = {}
+    for c in range(ctas):
+        assert lib.hogatt_plan_ranges(th, units, ctas, c, 0, rng) == 0
+        a, b = rng[0], rng[1]
+        assert a == covered and b > a, "ranges must be contiguous and non-empty"
+        covered = b
+        for u in range(a // th, (b - 1) // th + 1):
+            owners.setdefault(u, []).append(c)
+    assert covered == n
+    for u in range(units):
+        assert lib.hogatt_plan_ranges(th, units, ctas, 0, u, rng) == 0
+        first, count = rng[2], rng[3]
+        assert owners[u] == list(range(first, first + count)), "partial slots must match the CTAs that touch the unit"
+        assert count <= parts_bound, "more partials than the workspace reserves"

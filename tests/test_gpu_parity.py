@@ -1,0 +1,151 @@
+"""GPU parity: the CUDA path (through the C ABI) against the reference's outputs and the oracle."""
+import numpy as np
+import pytest
+import torch
+
+from inference_lib_b200 import _cabi
+from inference_lib_b200 import workloads as wl
+from oracle import hogwild_oracle as oracle
+from tests.gpu_util import check_against, run_cabi
+
+pytestmark = pytest.mark.gpu
+
+CFG5_SLICE = (slice(None), slice(None, None, 8), slice(None, None, 4), slice(None))
+
+
+def _kernels_for(p):
+    ks = []
+    if p.dtype != torch.float32 and p.E == p.Ev and p.E in (64, 128):
+        ks.append(_cabi.KERNEL_MMA)
+    if p.Ev in (32, 64, 128, 256):
+        ks.append(_cabi.KERNEL_FMA)
+    return ks
+
+
+@pytest.mark.parametrize("name", ["cfg1", "cfg2", "cfg3", "target", "cfg4"])
+def test_baseline_shapes_match_reference(golden, name):
+    p = wl.baseline_problem(name)
+    r = run_cabi(p)
+    assert r.rc == 0 and r.status == 0
+    check_against(r.out, golden[f"{name}/out"], p.dtype, what=name)
+
+
+def test_causal_chunk_config_matches_reference(golden):
+    p = wl.baseline_problem("cfg5", seed=2)
+    r = run_cabi(p)
+    assert r.rc == 0 and r.status == 0
+    check_against(r.out[CFG5_SLICE], golden["cfg5_g2/out"], p.dtype, what="cfg5 group 2")
+
+
+@pytest.mark.parametrize("name", sorted(wl.EDGE_CASES))
+def test_edge_cases_match_reference_on_every_eligible_kernel(golden, name):
+    p = wl.edge_problem(name)
+    kernels = _kernels_for(p)
+    assert kernels
+    for k in kernels:
+        r = run_cabi(p, kernel=k, want_rq=True)
+        assert r.rc == 0 and r.status == 0, (name, k, r.rc, r.status)
+        check_against(r.out, golden[f"{name}/out"], p.dtype, what=f"{name} kernel {k}")
+        if f"{name}/rq" in golden.files:
+            assert np.array_equal(r.rq.float().cpu().numpy(), golden[f"{name}/rq"]), "rotated queries must be bit-exact"
+
+
+@pytest.mark.parametrize("name", ["ragged_bf16", "causal_chunk_bf16", "ragged_f32", "hidden_and_partial_bf16",
+                                  "split_many_bf16", "many_rows_bf16", "row_blocks_bf16"])
+@pytest.mark.parametrize("max_ctas", [1, 2, 3, 7, 31])
+def test_result_does_not_depend_on_the_grid(golden, name, max_ctas):
+    """Any number of CTAs cuts the tile list differently; the merged result must stay within tolerance."""
+    p = wl.edge_problem(name)
+    for k in _kernels_for(p):
+        r = run_cabi(p, kernel=k, max_ctas=max_ctas)
+        assert r.rc == 0 and r.status == 0
+        check_against(r.out, golden[f"{name}/out"], p.dtype, what=f"{name} ctas {max_ctas} kernel {k}")
+
+
+@pytest.mark.parametrize("name", ["ragged_bf16", "cfg1", "causal_chunk_bf16", "gqa5_bf16"])
+def test_prerotated_entry_point_equals_fused(golden, name):
+    p = wl.baseline_problem(name) if name.startswith("cfg") else wl.edge_problem(name)
+    rq = oracle.rotate_queries(p.queries, p.cos, p.sin)
+    a = run_cabi(p, fused=True)
+    b = run_cabi(p, fused=False, pre_rotated=rq)
+    assert a.rc == 0 and b.rc == 0
+    assert torch.equal(a.out, b.out), "same rounded queries, same kernel: results must be identical"
+    check_against(b.out, golden[f"{name}/out"], p.dtype, what=name)
+
+
+def test_mma_and_fma_kernels_agree():
+    p = wl.edge_problem("split_many_bf16")
+    a = run_cabi(p, kernel=_cabi.KERNEL_MMA)
+    b = run_cabi(p, kernel=_cabi.KERNEL_FMA)
+    assert a.rc == 0 and b.rc == 0
+    assert (a.out.float() - b.out.float()).abs().max() <= 1e-2
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_random_shapes_against_oracle(seed):
+    rng = np.random.default_rng(seed)
+    dtype = [torch.bfloat16, torch.float16, torch.float32][seed % 3]
+    E = int(rng.choice([64, 128]))
+    W, S = int(rng.integers(1, 5)), int(rng.integers(1, 4))
+    Hkv, G = int(rng.integers(1, 4)), int(rng.choice([1, 2, 4, 7]))
+    lengths = [int(rng.integers(1, 400))] + [int(rng.integers(S, 70)) for _ in range(W)]
+    p = wl.make_problem(f"rand{seed}", W=W, Hq=Hkv * G, Hkv=Hkv, E=E, S=S, lengths=lengths, theta=1e4, dtype=dtype,
+                        seed=100 + seed)
+    ref, _ = oracle.fused(p.queries, p.cos, p.sin, p.locations, p.keys, p.values, p.scale)
+    for k in _kernels_for(p):
+        r = run_cabi(p, kernel=k)
+        assert r.rc == 0 and r.status == 0
+        check_against(r.out, ref.numpy(), p.dtype, what=f"seed {seed} kernel {k}")
+
+
+def test_device_lengths_shorter_than_the_tensors():
+    """fragment_lengths (device) may be shorter than the tensors' row extent: only that prefix is visible."""
+    p = wl.edge_problem("ragged_bf16")
+    short = torch.tensor([20, 1, 4, 77], dtype=torch.int32)
+    q = wl.Problem(**{**p.__dict__, "fragment_lengths": short})
+    keys = [k[:, :, :int(n)] for k, n in zip(p.keys, short)]
+    vals = [v[:, :, :int(n)] for v, n in zip(p.values, short)]
+    ref, _ = oracle.fused(p.queries, p.cos, p.sin, p.locations, keys, vals, p.scale)
+    r = run_cabi(q)
+    assert r.rc == 0 and r.status == 0
+    check_against(r.out, ref.numpy(), p.dtype)
+
+
+def test_rope_entry_point_is_bit_exact(golden):
+    import ctypes as C
+    lib = _cabi.load()
+    for name in ("cfg1", "ragged_f16", "ragged_bf16", "partial_rotary_bf16", "causal_chunk_bf16"):
+        p = wl.baseline_problem(name) if name.startswith("cfg") else wl.edge_problem(name)
+        d = p.to("cuda:0")
+        rq = torch.empty((p.F, p.W, p.Hq, p.S, p.E), dtype=p.dtype, device="cuda:0")
+        rc = lib.hogatt_rope_launch(rq.data_ptr(), d.queries.data_ptr(), d.cos.data_ptr(), d.sin.data_ptr(), p.F, p.W,
+                                    p.Hq, p.S, p.E, p.cos.shape[-1], _cabi.dtype_code(p.dtype),
+                                    C.c_void_p(torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize()
+        assert rc == 0
+        assert np.array_equal(rq.float().cpu().numpy(), golden[f"{name}/rq"])
+
+
+def test_bad_arguments_are_refused_without_launching():
+    p = wl.edge_problem("ragged_bf16")
+    d = p.to("cuda:0")
+    out = torch.zeros((p.W, p.Hq, p.S, p.Ev), dtype=p.dtype, device="cuda:0")
+    ws = torch.zeros(1 << 20, dtype=torch.uint8, device="cuda:0")
+    mk = lambda **kw: _cabi.bind(**{**dict(out=out, queries=d.queries, locations=d.locations, keys=d.keys, values=d.values,
+                                           scale=p.scale, cos=d.cos, sin=d.sin, workspace=ws), **kw})
+    bp = mk(); bp.struct.workspace_bytes = 16
+    assert _cabi.launch(bp) == -7
+    bp = mk(); bp.struct.Hkv = 3
+    assert _cabi.launch(bp) == -2
+    bp = mk(); bp.struct.F = 1000
+    assert _cabi.launch(bp) == -5
+    bp = mk(); bp.struct.dtype = 9
+    assert _cabi.launch(bp) == -4
+    bp = mk(kernel=_cabi.KERNEL_MMA); bp.struct.dtype = _cabi.F32
+    assert _cabi.launch(bp) == -9
+    bp = mk(); bp.struct.queries = d.queries.data_ptr() + 2
+    assert _cabi.launch(bp) == -6
+    bp = mk(); bp.struct.out = None
+    assert _cabi.launch(bp) == -1
+    torch.cuda.synchronize()
+    assert (out == 0).all(), "a refused call must not touch the output"
