@@ -215,13 +215,13 @@ def run_ours(args):
         # isolated, cold call: one launch between events, L2 flushed by a 256 MiB write before it
         flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
         iso = []
-        for i in range(12):
+        for i in range(0 if args.no_isolated else 12):
             flush.fill_(i)
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record(); calls[i % len(calls)].launch(torch.cuda.current_stream().cuda_stream); e1.record()
             torch.cuda.synchronize()
             iso.append(e0.elapsed_time(e1) * 1e3)
-        iso_us = statistics.median(iso[2:])
+        iso_us = statistics.median(iso[2:]) if iso else float("nan")
 
     t = torch.tensor([secs, secs_attn or 0.0], dtype=torch.float64, device=device)
     if dist:
@@ -231,7 +231,7 @@ def run_ours(args):
     us_per_call = secs / n_calls * 1e6
     value = bytes_per_call * n_calls / secs / 1e12
 
-    e2e = measure_e2e(args, full, device, dist, world) if True else None
+    e2e = None if args.no_e2e else measure_e2e(args, full, device, dist, world)
 
     if rank != 0:
         if dist:
@@ -376,6 +376,8 @@ def main():
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
+    ap.add_argument("--no-isolated", action="store_true", help="skip the isolated cold-call leg (profiling runs)")
     args = ap.parse_args()
     if args.workload == "cfg4":
         args.layers = min(args.layers, 4)          # 570 MB of KV per layer

@@ -1,5 +1,6 @@
 // C ABI of libhogatt_b200.so (declared in include/hogatt.h): argument validation, kernel choice,
 // workspace carving and launches.  No allocation, no synchronisation, no hidden static buffers.
+#include <algorithm>
 #include <atomic>
 #include <cstdio>
 #include <cstring>
@@ -273,9 +274,9 @@ int attention_launch(const hogatt_problem* p, bool fused, cudaStream_t stream) {
         if (rows < 0) return HOGATT_ERR_BAD_SHAPE;
         if (rows > 0 && (!p->key_fragments[f] || !p->value_fragments[f])) return HOGATT_ERR_NULL_POINTER;
         if (!aligned16(p->key_fragments[f]) || !aligned16(p->value_fragments[f])) return HOGATT_ERR_MISALIGNED;
-        args.ft.k[f] = p->key_fragments[f];
-        args.ft.v[f] = p->value_fragments[f];
-        args.ft.rows[f] = rows;
+        args.ft.e[f].k = p->key_fragments[f];
+        args.ft.e[f].v = p->value_fragments[f];
+        args.ft.e[f].rows = rows;
     }
 
     switch (p->dtype) {
@@ -338,7 +339,8 @@ int hogatt_rope_launch(void* rq, const void* queries, const float* cosines, cons
         return HOGATT_ERR_BAD_SHAPE;
     const int64_t rows = (int64_t)F * W * Hq * S;
     if (rows > (1 << 30)) return HOGATT_ERR_TOO_LARGE;
-    const unsigned blocks = (unsigned)((rows + 3) / 4);
+    const int64_t work = rows * ((dtype != HOGATT_F32 && E % 8 == 0) ? E / 8 : E);      // chunks or channels
+    const unsigned blocks = (unsigned)std::min<int64_t>((work + 127) / 128, 1 << 16);
     switch (dtype) {
         case HOGATT_F32:
             rope_kernel<float><<<blocks, 128, 0, stream>>>((float*)rq, (const float*)queries, cosines, sines, F, W, Hq, S, E, rotary_dim);
@@ -354,6 +356,16 @@ int hogatt_rope_launch(void* rq, const void* queries, const float* cosines, cons
     HOGATT_CUDA_OK(cudaGetLastError());
     return HOGATT_OK;
 }
+
+#ifdef HOGATT_TIMELINE
+// Debug builds only: copy out the timeline of the instrumented CTA (see hogatt_device.cuh).
+int hogatt_debug_read_timeline(long long* times /*[2][1024]*/, int* tags /*[2][1024]*/, int* counts /*[2]*/) {
+    HOGATT_CUDA_OK(cudaMemcpyFromSymbol(times, g_timeline, sizeof(long long) * 2048));
+    HOGATT_CUDA_OK(cudaMemcpyFromSymbol(tags, g_timeline_tag, sizeof(int) * 2048));
+    HOGATT_CUDA_OK(cudaMemcpyFromSymbol(counts, g_timeline_n, sizeof(int) * 2));
+    return HOGATT_OK;
+}
+#endif
 
 int hogatt_plan_describe(const hogatt_problem* p, const int32_t* visible_rows, int32_t num_sms, int32_t plan[8]) {
     Resolved r;

@@ -16,10 +16,14 @@ namespace hogatt {
 // table, so a call needs no host->device copy of pointers (the reference copies a pointer table
 // per call, src/binding.cu:79-103).
 // ---------------------------------------------------------------------------------------------
+struct FragmentEntry {                     // 24 bytes: one constant-cache line holds a fragment's whole entry
+    const void* k;                         // [Hkv, rows, E]
+    const void* v;                         // [Hkv, rows, Ev]
+    int rows;                              // token extent of the tensors (head stride = rows * E)
+    int pad_;
+};
 struct FragmentTable {
-    const void* k[HOGATT_MAX_FRAGMENTS];   // [Hkv, rows, E]
-    const void* v[HOGATT_MAX_FRAGMENTS];   // [Hkv, rows, Ev]
-    int rows[HOGATT_MAX_FRAGMENTS];        // token extent of the tensors (head stride = rows * E)
+    FragmentEntry e[HOGATT_MAX_FRAGMENTS];
 };
 
 struct KernelArgs {
@@ -51,6 +55,26 @@ enum DeviceStatusBits : int {
     STATUS_DRAIN_TIMEOUT = 8          // copies still in flight when the CTA wanted to leave
 };
 
+// Optional timeline for kernel tuning (compile with -DHOGATT_TIMELINE=<cta>): lane 0 of two warps of
+// one CTA records clock64() at named points into a device array that a debug entry point copies out.
+#ifdef HOGATT_TIMELINE
+__device__ long long g_timeline[2][1024];
+__device__ int g_timeline_tag[2][1024];
+__device__ int g_timeline_n[2];
+#define HOGATT_TL_DECL int tlc__ = 0
+#define HOGATT_TL(who, tag)                                                              \
+    do {                                                                                 \
+        if (blockIdx.x == HOGATT_TIMELINE && (threadIdx.x & 31) == 0 && tlc__ < 1024) {  \
+            g_timeline[who][tlc__] = clock64();                                          \
+            g_timeline_tag[who][tlc__] = (tag);                                          \
+            g_timeline_n[who] = ++tlc__;                                                 \
+        }                                                                                \
+    } while (0)
+#else
+#define HOGATT_TL_DECL
+#define HOGATT_TL(who, tag)
+#endif
+
 // ---------------------------------------------------------------------------------------------
 // Scalar type helpers
 // ---------------------------------------------------------------------------------------------
@@ -71,19 +95,21 @@ template <> struct Scalar<__nv_bfloat16> {
 // One rotated query channel, computed exactly like the reference's eager path: both products are
 // rounded to fp32 before they are added (no fused multiply-add), and the caller rounds the sum
 // to the storage type (python/hogwild/attention.py:84-90; src/rope.cuh:24-46, src/q_rope.h:17-25).
-// `q` points at the un-rotated row, `c`/`s` at that row's table for the fragment.
+// `q` points at the un-rotated row, `c`/`s` at that row's table for the fragment.  Written without
+// branches (selects only) so that the loads of many channels can be issued back to back instead of
+// one dependent round trip per channel.
 template <class T>
 __device__ __forceinline__ float rope_channel(const T* __restrict__ q, const float* __restrict__ c,
                                               const float* __restrict__ s, int e, int R) {
-    const float x = Scalar<T>::to_float(q[e]);
-    if (e >= R) return x;
     const int half = R >> 1;
-    if (e < half) {
-        const float y = Scalar<T>::to_float(q[e + half]);
-        return __fsub_rn(__fmul_rn(x, c[e]), __fmul_rn(y, s[e]));
-    }
-    const float y = Scalar<T>::to_float(q[e - half]);
-    return __fadd_rn(__fmul_rn(x, c[e]), __fmul_rn(y, s[e]));
+    const bool rot = e < R, lo = e < half;
+    const int pe = rot ? (lo ? e + half : e - half) : e;    // partner channel
+    const int te = rot ? e : 0;                              // table index (always in range)
+    const float x = Scalar<T>::to_float(q[e]);
+    const float y = Scalar<T>::to_float(q[pe]);
+    const float a = __fmul_rn(x, c[te]), b = __fmul_rn(y, s[te]);
+    const float r = lo ? __fsub_rn(a, b) : __fadd_rn(a, b);
+    return rot ? r : x;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -215,6 +241,115 @@ __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Two adjacent rotated channels (e even) of a 16-bit query row, packed for an MMA A-fragment.
+// Needs R % 4 == 0 so that e and e + 1 lie on the same side of R/2 and of R; 4- and 8-byte loads.
+template <class T>
+__device__ __forceinline__ uint32_t rope_pair(const T* __restrict__ q, const float* __restrict__ c,
+                                              const float* __restrict__ s, int e, int R) {
+    const int half = R >> 1;
+    const bool rot = e < R, lo = e < half;
+    const int pe = rot ? (lo ? e + half : e - half) : e;
+    const int te = rot ? e : 0;
+    const uint32_t xr = *reinterpret_cast<const uint32_t*>(q + e);
+    const uint32_t yr = *reinterpret_cast<const uint32_t*>(q + pe);
+    const float2 cv = *reinterpret_cast<const float2*>(c + te);
+    const float2 sv = *reinterpret_cast<const float2*>(s + te);
+    const T* xp = reinterpret_cast<const T*>(&xr);
+    const T* yp = reinterpret_cast<const T*>(&yr);
+    const float x0 = Scalar<T>::to_float(xp[0]), x1 = Scalar<T>::to_float(xp[1]);
+    const float y0 = Scalar<T>::to_float(yp[0]), y1 = Scalar<T>::to_float(yp[1]);
+    const float a0 = __fmul_rn(x0, cv.x), b0 = __fmul_rn(y0, sv.x);
+    const float a1 = __fmul_rn(x1, cv.y), b1 = __fmul_rn(y1, sv.y);
+    const float r0 = lo ? __fsub_rn(a0, b0) : __fadd_rn(a0, b0);
+    const float r1 = lo ? __fsub_rn(a1, b1) : __fadd_rn(a1, b1);
+    return rot ? pack2<T>(r0, r1) : xr;
+}
+
+// Eight adjacent rotated channels [8*ch, 8*ch + 8) of a 16-bit query row as one 16-byte vector.
+// All loads are 16-byte vectors and independent of each other, so a thread can keep several chunks
+// in flight in a single memory round trip.  Needs R % 16 == 0 (the partner of a chunk is a whole
+// chunk) and 16-byte aligned table rows.
+template <class T>
+__device__ __forceinline__ uint4 rotate_chunk(const T* __restrict__ q, const float* __restrict__ c,
+                                              const float* __restrict__ s, int ch, int R) {
+    const int e0 = ch * 8, half = R >> 1;
+    const bool rot = e0 < R, lo = e0 < half;
+    const int pe = rot ? (lo ? e0 + half : e0 - half) : e0;
+    const int te = rot ? e0 : 0;
+    const uint4 xr = *reinterpret_cast<const uint4*>(q + e0);
+    const uint4 yr = *reinterpret_cast<const uint4*>(q + pe);
+    const float4 c0 = *reinterpret_cast<const float4*>(c + te), c1 = *reinterpret_cast<const float4*>(c + te + 4);
+    const float4 s0 = *reinterpret_cast<const float4*>(s + te), s1 = *reinterpret_cast<const float4*>(s + te + 4);
+    const T* x = reinterpret_cast<const T*>(&xr);
+    const T* y = reinterpret_cast<const T*>(&yr);
+    const float cv[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+    uint4 out;
+    uint32_t* o = reinterpret_cast<uint32_t*>(&out);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        float r[2];
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+            const float a = __fmul_rn(Scalar<T>::to_float(x[2 * i + k]), cv[2 * i + k]);
+            const float b = __fmul_rn(Scalar<T>::to_float(y[2 * i + k]), sv[2 * i + k]);
+            r[k] = lo ? __fsub_rn(a, b) : __fadd_rn(a, b);
+        }
+        o[i] = pack2<T>(r[0], r[1]);
+    }
+    return rot ? out : xr;
+}
+
+// True when rotate_chunk can be used for this call.
+__device__ __forceinline__ bool chunked_rope_ok(const float* c, const float* s, int R, int E) {
+    return (R & 15) == 0 && (E & 7) == 0 && ((((uintptr_t)c) | ((uintptr_t)s)) & 15u) == 0;
+}
+
+// rq[f,w,h,s,:] for all rows, dealt over the participating threads of the whole grid
+// (`gthread` of `gthreads`).  Used when the caller wants the rotated queries back.  16-bit types
+// take the chunked path: one 16-byte chunk per thread per step, one memory round trip.
+template <class T>
+__device__ __forceinline__ void write_rotated_queries(const void* qv, void* rqv, const float* cos, const float* sin,
+                                                      int F, int W, int Hq, int S, int E, int R, int gthread,
+                                                      int gthreads) {
+    T* __restrict__ rq = static_cast<T*>(rqv);
+    const T* __restrict__ q = static_cast<const T*>(qv);
+    const int rows = F * W * Hq * S;
+    if constexpr (sizeof(T) == 2) {
+      if (chunked_rope_ok(cos, sin, R, E)) {
+        const int cpr = E >> 3;
+        const int items = rows * cpr;
+#pragma unroll 2
+        for (int item = gthread; item < items; item += gthreads) {
+            const int row = item / cpr, ch = item - row * cpr;
+            const int s = row % S;
+            int t = row / S;
+            const int h = t % Hq;
+            t /= Hq;
+            const int w = t % W, f = t / W;
+            const T* qrow = q + ((size_t)(w * Hq + h) * S + s) * E;
+            const size_t tab = ((size_t)(f * W + w) * S + s) * R;
+            const uint4 val = rotate_chunk<T>(qrow, cos + tab, sin + tab, ch, R);
+            *reinterpret_cast<uint4*>(rq + (size_t)row * E + ch * 8) = val;
+        }
+        return;
+      }
+    }
+    const int64_t items = (int64_t)rows * E;
+#pragma unroll 4
+    for (int64_t item = gthread; item < items; item += gthreads) {
+        const int row = (int)(item / E), e = (int)(item - (int64_t)row * E);
+        const int s = row % S;
+        int t = row / S;
+        const int h = t % Hq;
+        t /= Hq;
+        const int w = t % W, f = t / W;
+        const T* qrow = q + ((size_t)(w * Hq + h) * S + s) * E;
+        const size_t tab = ((size_t)(f * W + w) * S + s) * R;
+        rq[item] = Scalar<T>::from_float(rope_channel<T>(qrow, cos + tab, sin + tab, e, R));
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // Visible lengths and the tile prefix, built once per CTA in shared memory.
 //   vis[f]  = clamp(max over (w,s) of loc[f,w,s] + 1, 0, min(rows_f, flen[f]))
@@ -226,14 +361,12 @@ __device__ __forceinline__ void build_tile_prefix(const KernelArgs& a, int tile_
     const int per = a.W * a.S;
     for (int f = warp; f < a.F; f += nwarps) {
         int top = -1;
+        int cap = a.ft.e[f].rows;
+        if (a.flen) cap = min(cap, a.flen[f]);            // issued together with the loads below
         for (int i = lane; i < per; i += 32) top = max(top, a.loc[f * per + i]);
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) top = max(top, __shfl_xor_sync(0xffffffffu, top, o));
-        if (lane == 0) {
-            int cap = a.ft.rows[f];
-            if (a.flen) cap = min(cap, a.flen[f]);
-            vis[f] = max(0, min(top + 1, cap));
-        }
+        if (lane == 0) vis[f] = max(0, min(top, cap - 1) + 1);
     }
     __syncthreads();
     if (threadIdx.x == 0) {

@@ -24,29 +24,6 @@ __host__ __device__ inline size_t fma_smem_bytes(int E, int Ev, int F) {
     return floats * sizeof(float) + ints * sizeof(int);
 }
 
-// rq[f,w,h,s,:] for the rows this warp is responsible for (rows are dealt round-robin over all
-// warps of the grid).  Used when the caller wants the rotated queries back.
-template <class T>
-__device__ __forceinline__ void write_rotated_queries(const KernelArgs& a, int global_warp, int total_warps) {
-    const int lane = threadIdx.x & 31;
-    const int rows = a.F * a.W * a.Hq * a.S;
-    T* __restrict__ rq = static_cast<T*>(a.rq);
-    const T* __restrict__ q = static_cast<const T*>(a.q);
-    for (int row = global_warp; row < rows; row += total_warps) {
-        int s = row % a.S;
-        int t = row / a.S;
-        const int h = t % a.Hq;
-        t /= a.Hq;
-        const int w = t % a.W;
-        const int f = t / a.W;
-        const T* qrow = q + ((size_t)(w * a.Hq + h) * a.S + s) * a.E;
-        const float* c = a.cos + ((size_t)(f * a.W + w) * a.S + s) * a.R;
-        const float* sn = a.sin + ((size_t)(f * a.W + w) * a.S + s) * a.R;
-        T* dst = rq + (size_t)row * a.E;
-        for (int e = lane; e < a.E; e += 32) dst[e] = Scalar<T>::from_float(rope_channel<T>(qrow, c, sn, e, a.R));
-    }
-}
-
 template <class T, int EV>
 __global__ void __launch_bounds__(kFmaThreads) fma_attention_kernel(const __grid_constant__ KernelArgs a) {
     constexpr int VEC = 16 / sizeof(T);
@@ -77,7 +54,8 @@ __global__ void __launch_bounds__(kFmaThreads) fma_attention_kernel(const __grid
         a.header[1] = ctas;
     }
     if (a.rq != nullptr && a.cos != nullptr)
-        write_rotated_queries<T>(a, blockIdx.x * (kFmaThreads / 32) + warp, gridDim.x * (kFmaThreads / 32));
+        write_rotated_queries<T>(a.q, a.rq, a.cos, a.sin, a.F, a.W, a.Hq, a.S, a.E, a.R, blockIdx.x * kFmaThreads + tid,
+                                 gridDim.x * kFmaThreads);
     if ((int)blockIdx.x >= ctas) return;
 
     const int64_t t0 = cta_first_tile(blockIdx.x, N, ctas), t1 = cta_first_tile(blockIdx.x + 1, N, ctas);
@@ -108,6 +86,7 @@ __global__ void __launch_bounds__(kFmaThreads) fma_attention_kernel(const __grid
         if (f != cur_f) {
             cur_f = f;
             // (re)build the 16 query rows for this fragment: rotate, round to the storage type
+#pragma unroll 4
             for (int idx = tid; idx < kFmaRows * E; idx += kFmaThreads) {
                 const int r = idx / E, e = idx - r * E;
                 const int gr = rb * kFmaRows + r;
@@ -142,9 +121,9 @@ __global__ void __launch_bounds__(kFmaThreads) fma_attention_kernel(const __grid
 
         // ---- stage the K and V rows of this tile as fp32 (rows are consecutive in memory) ----
         {
-            const size_t row0 = (size_t)hkv * a.ft.rows[f] + tok0;
-            const T* ksrc = static_cast<const T*>(a.ft.k[f]) + row0 * E;
-            const T* vsrc = static_cast<const T*>(a.ft.v[f]) + row0 * EV;
+            const size_t row0 = (size_t)hkv * a.ft.e[f].rows + tok0;
+            const T* ksrc = static_cast<const T*>(a.ft.e[f].k) + row0 * E;
+            const T* vsrc = static_cast<const T*>(a.ft.e[f].v) + row0 * EV;
             const int kvecs = ntok * E / VEC;
             for (int i = tid; i < kvecs; i += kFmaThreads) {
                 const int4 raw = __ldg(reinterpret_cast<const int4*>(ksrc) + i);

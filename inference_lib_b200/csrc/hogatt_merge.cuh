@@ -31,62 +31,78 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const __grid_co
         T* dst = out + ((size_t)(id.w * a.Hq + hkv * a.G + id.g) * a.S + id.s) * Ev;
         const size_t slot0 = (size_t)u * a.parts_per_unit;
 
-        float M = -INFINITY;
-        for (int p = lane; p < count; p += 32) M = fmaxf(M, a.ws_m[(slot0 + p) * RPB + row]);
+        // statistics of up to 32 partials live one per lane (more are folded in by a strided loop);
+        // the weights are then broadcast by shuffle, so the O loads below do not depend on memory
+        float mp = -INFINITY, lp = 0.f;
+        for (int p = lane; p < count; p += 32) {
+            const float m2 = a.ws_m[(slot0 + p) * RPB + row], l2 = a.ws_l[(slot0 + p) * RPB + row];
+            if (p < 32) { mp = m2; lp = l2; }
+        }
+        float M = mp;
+        for (int p = lane + 32; p < count; p += 32) M = fmaxf(M, a.ws_m[(slot0 + p) * RPB + row]);
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
-
-        float den = 0.f;
-        if (M != -INFINITY) {
-            for (int p = lane; p < count; p += 32)
+        const float wp = (M == -INFINITY) ? 0.f : exp2f(mp - M);      // weight of partial `lane`
+        float den = wp * lp;
+        if (M != -INFINITY)
+            for (int p = lane + 32; p < count; p += 32)
                 den += a.ws_l[(slot0 + p) * RPB + row] * exp2f(a.ws_m[(slot0 + p) * RPB + row] - M);
 #pragma unroll
-            for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
-        }
+        for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
         const bool blind = !(den > 0.f);
         const float inv = blind ? 0.f : 1.f / den;
 
-        for (int e = lane * 4; e < Ev; e += 128) {
+        for (int e0 = 0; e0 < Ev; e0 += 128) {          // uniform trip count: the shuffles need every lane
+            const int e = e0 + lane * 4;
+            const bool mine = e < Ev;
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (!blind) {
-                for (int p = 0; p < count; ++p) {
-                    const float wgt = exp2f(a.ws_m[(slot0 + p) * RPB + row] - M);
-                    const float4 x = *reinterpret_cast<const float4*>(a.ws_o + ((slot0 + p) * RPB + row) * Ev + e);
-                    acc.x = fmaf(x.x, wgt, acc.x);
-                    acc.y = fmaf(x.y, wgt, acc.y);
-                    acc.z = fmaf(x.z, wgt, acc.z);
-                    acc.w = fmaf(x.w, wgt, acc.w);
+            const float* src = a.ws_o + (slot0 * RPB + row) * Ev + (mine ? e : 0);
+            const size_t pstride = (size_t)RPB * Ev;
+            const int c32 = min(count, 32);
+            for (int p0 = 0; p0 < c32; p0 += 8) {
+                float4 x[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k)            // eight independent 16-byte loads in flight
+                    x[k] = (p0 + k < c32) ? *reinterpret_cast<const float4*>(src + (p0 + k) * pstride)
+                                          : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const float wgt = __shfl_sync(0xffffffffu, wp, (p0 + k) & 31);
+                    acc.x = fmaf(x[k].x, wgt, acc.x);
+                    acc.y = fmaf(x[k].y, wgt, acc.y);
+                    acc.z = fmaf(x[k].z, wgt, acc.z);
+                    acc.w = fmaf(x[k].w, wgt, acc.w);
                 }
             }
-            dst[e + 0] = Scalar<T>::from_float(acc.x * inv);
-            dst[e + 1] = Scalar<T>::from_float(acc.y * inv);
-            dst[e + 2] = Scalar<T>::from_float(acc.z * inv);
-            dst[e + 3] = Scalar<T>::from_float(acc.w * inv);
+            for (int p = 32; p < count; ++p) {
+                const float wgt = blind ? 0.f : exp2f(a.ws_m[(slot0 + p) * RPB + row] - M);
+                const float4 x = *reinterpret_cast<const float4*>(src + p * pstride);
+                acc.x = fmaf(x.x, wgt, acc.x);
+                acc.y = fmaf(x.y, wgt, acc.y);
+                acc.z = fmaf(x.z, wgt, acc.z);
+                acc.w = fmaf(x.w, wgt, acc.w);
+            }
+            if (blind) acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (mine) {
+                dst[e + 0] = Scalar<T>::from_float(acc.x * inv);
+                dst[e + 1] = Scalar<T>::from_float(acc.y * inv);
+                dst[e + 2] = Scalar<T>::from_float(acc.z * inv);
+                dst[e + 3] = Scalar<T>::from_float(acc.w * inv);
+            }
         }
     }
 }
 
-// rq[f,w,h,s,:] = rope(q[w,h,s,:], cos[f,w,s,:], sin[f,w,s,:]); one warp per output row.
-// Replaces rope_kernel (src/rope.cuh:2-52), which uses one thread per channel and one CTA per row.
+// rq[f,w,h,s,:] = rope(q[w,h,s,:], cos[f,w,s,:], sin[f,w,s,:]).
+// Replaces rope_kernel (src/rope.cuh:2-52), which uses one thread per channel and one CTA per row;
+// here a thread produces a 16-byte chunk of a row from 16-byte loads.
 template <class T>
 __global__ void __launch_bounds__(128) rope_kernel(T* __restrict__ rq, const T* __restrict__ q,
                                                    const float* __restrict__ cosines,
                                                    const float* __restrict__ sines, int F, int W, int Hq, int S,
                                                    int E, int R) {
-    const int lane = threadIdx.x & 31;
-    const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
-    if (row >= F * W * Hq * S) return;
-    int s = row % S;
-    int t = row / S;
-    const int h = t % Hq;
-    t /= Hq;
-    const int w = t % W;
-    const int f = t / W;
-    const T* qrow = q + ((size_t)(w * Hq + h) * S + s) * E;
-    const float* c = cosines + ((size_t)(f * W + w) * S + s) * R;
-    const float* sn = sines + ((size_t)(f * W + w) * S + s) * R;
-    T* dst = rq + (size_t)row * E;
-    for (int e = lane; e < E; e += 32) dst[e] = Scalar<T>::from_float(rope_channel<T>(qrow, c, sn, e, R));
+    write_rotated_queries<T>(q, rq, cosines, sines, F, W, Hq, S, E, R, blockIdx.x * blockDim.x + threadIdx.x,
+                             gridDim.x * blockDim.x);
 }
 
 }  // namespace hogatt

@@ -36,28 +36,32 @@ template <int HD, int MT>
 struct MmaCfg {
     static constexpr int NCW = (MT == 1) ? 4 : 8;        // consumer warps
     static constexpr int NSLICE = NCW / MT;              // warps sharing one m-tile, each takes a slice of the keys
-    static constexpr int GT = (HD == 128) ? 8 : 16;      // keys per group
+    static constexpr int GT = (HD == 128) ? 16 : 32;     // keys per group (one 4 KiB bulk copy)
     static constexpr int TILE = 8 * GT;                  // keys per stage
     static constexpr int ROWB = HD * 2;                  // bytes per key row
     static constexpr int GROUP_STRIDE = GT * ROWB + 16;
     static constexpr int KV_BYTES = 8 * GROUP_STRIDE;
     static constexpr int STAGE_BYTES = 2 * KV_BYTES;
-    static constexpr int NSTAGE = 6;
+    static constexpr int NSTAGE = 3;
     static constexpr int NT_S = GT / NSLICE;             // 8-key n-tiles per warp per stage
     static constexpr int NT_O = HD / 8;                  // output n-tiles
     static constexpr int KSTEPS = HD / 16;
     static constexpr int THREADS = (NCW + 1) * 32;
     static constexpr int RPB = 16 * MT;                  // query rows per CTA
     static constexpr int SLOT_FLOATS = NT_O * 4 * 32;    // one warp's accumulators
+    static constexpr int QPITCH = ROWB + 16;             // bytes per staged query row (padding: conflict-free ldmatrix)
+    static constexpr int QBYTES = RPB * QPITCH;
     static_assert(NT_S >= 2 && NT_S % 2 == 0, "a warp's slice must hold whole k16 steps");
-    static_assert((NCW / 2) * SLOT_FLOATS * 4 <= STAGE_BYTES, "fold scratch must fit in one stage");
+    static_assert(NCW * SLOT_FLOATS * 4 <= STAGE_BYTES, "fold scratch must fit in one stage");
+    static_assert(NT_O % NSLICE == 0, "output columns must split evenly over the slices");
 };
 
 template <int HD, int MT>
 __host__ __device__ inline size_t mma_smem_bytes(int F) {
     using C = MmaCfg<HD, MT>;
-    return 128 /* alignment slack */ + (size_t)C::NSTAGE * C::STAGE_BYTES + (size_t)(C::NCW / 2) * 32 * 4 * 4 /* stats */ +
-           (2 * C::NSTAGE + 1) * 8 /* barriers */ + 16 /* abort flag */ + ((size_t)2 * F + 1) * 4;
+    return 128 /* alignment slack */ + (size_t)C::NSTAGE * C::STAGE_BYTES + C::QBYTES +
+           (size_t)C::NCW * 32 * 4 * 4 /* stats */ + (2 * C::NSTAGE + 1) * 8 /* barriers */ + 16 /* abort flag */ +
+           ((size_t)2 * F + 1) * 4;
 }
 
 template <class T, int HD, int MT>
@@ -67,13 +71,16 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
     extern __shared__ unsigned char smem_dyn[];
     unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 127) & ~(uintptr_t)127);
     unsigned char* stages = base;
-    float* stats = reinterpret_cast<float*>(stages + (size_t)C::NSTAGE * C::STAGE_BYTES);   // [NCW/2][32][4]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(stats + (C::NCW / 2) * 32 * 4);
+    unsigned char* qtile = stages + (size_t)C::NSTAGE * C::STAGE_BYTES;                     // [RPB][QPITCH]
+    float* stats = reinterpret_cast<float*>(qtile + C::QBYTES);                             // [NCW][32][4]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(stats + C::NCW * 32 * 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * C::NSTAGE + 1);
     int* vis = const_cast<int*>(abort_flag) + 4;
     int* pre = vis + a.F;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    HOGATT_TL_DECL;
+    HOGATT_TL(warp == 0 ? 0 : 1, 1);
     const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * C::NSTAGE, cbar = full0 + 16 * C::NSTAGE;
     const uint32_t stage0 = smem_u32(stages);
 
@@ -88,6 +95,7 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
         fence_proxy_async_smem();
     }
     build_tile_prefix(a, C::TILE, vis, pre);     // ends with __syncthreads(): barriers are visible too
+    if (warp <= 1) HOGATT_TL(warp, 2);
 
     const int TH = pre[a.F];
     const int units = a.row_blocks * a.Hkv;
@@ -97,9 +105,16 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
         a.header[0] = TH;
         a.header[1] = ctas;
     }
-    if (a.rq != nullptr && a.cos != nullptr && warp > 0)
-        write_rotated_queries<T>(a, blockIdx.x * C::NCW + (warp - 1), gridDim.x * C::NCW);
-    if ((int)blockIdx.x >= ctas) return;
+    // The rotated-query output is written by the consumer threads of all CTAs.  CTAs with tiles do
+    // it after their first fragment prologue, while the first K/V tile is still in flight.
+    const bool want_rq = a.rq != nullptr && a.cos != nullptr;
+    if ((int)blockIdx.x >= ctas) {
+        if (want_rq && warp > 0)
+            write_rotated_queries<T>(a.q, a.rq, a.cos, a.sin, a.F, a.W, a.Hq, a.S, HD, a.R,
+                                     blockIdx.x * (C::NCW * 32) + tid - 32, gridDim.x * (C::NCW * 32));
+        return;
+    }
+    if (warp <= 1) HOGATT_TL(warp, 3);
 
     const int64_t t0 = cta_first_tile(blockIdx.x, N, ctas), t1 = cta_first_tile(blockIdx.x + 1, N, ctas);
 
@@ -131,8 +146,8 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
                 const int tg = min(C::GT, ntok - g * C::GT);
                 if (tg > 0) {
                     const bool is_v = lane >= 8;
-                    const unsigned char* src = static_cast<const unsigned char*>(is_v ? a.ft.v[f] : a.ft.k[f]) +
-                                               ((size_t)hkv * a.ft.rows[f] + tok0 + g * C::GT) * C::ROWB;
+                    const unsigned char* src = static_cast<const unsigned char*>(is_v ? a.ft.e[f].v : a.ft.e[f].k) +
+                                               ((size_t)hkv * a.ft.e[f].rows + tok0 + g * C::GT) * C::ROWB;
                     const uint32_t dst = stage0 + stage * C::STAGE_BYTES + (is_v ? C::KV_BYTES : 0) + g * C::GROUP_STRIDE;
                     if (use_evict_first)
                         bulk_load_hint(dst, src, (uint32_t)tg * C::ROWB, fullb, policy);
@@ -140,6 +155,7 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
                         bulk_load(dst, src, (uint32_t)tg * C::ROWB, fullb);
                 }
             }
+            HOGATT_TL(0, 100 + it);
             if (++j == TH) {
                 j = 0;
                 ++u;
@@ -204,31 +220,70 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
         const int f = fscan;
         if (f != cur_f) {
             cur_f = f;
-            // ---- per-fragment prologue: rotated query rows -> MMA A-fragments, visibility limits ----
-            const int hq_a = hkv * a.G + id_a.g, hq_b = hkv * a.G + id_b.g;
-            auto load_pair = [&](bool valid, const RowId& id, int hq, int e) -> uint32_t {
-                if (!valid) return 0u;
-                if (a.cos == nullptr) {
-                    const T* src = q + ((size_t)((f * a.W + id.w) * a.Hq + hq) * a.S + id.s) * HD + e;
-                    return *reinterpret_cast<const uint32_t*>(src);
-                }
-                const T* qrow = q + ((size_t)(id.w * a.Hq + hq) * a.S + id.s) * HD;
-                const size_t tab = ((size_t)(f * a.W + id.w) * a.S + id.s) * a.R;
-                const float x0 = rope_channel<T>(qrow, a.cos + tab, a.sin + tab, e, a.R);
-                const float x1 = rope_channel<T>(qrow, a.cos + tab, a.sin + tab, e + 1, a.R);
-                return pack2<T>(x0, x1);
-            };
-#pragma unroll
-            for (int kk = 0; kk < C::KSTEPS; ++kk) {
-                const int e = kk * 16 + qlane * 2;
-                qf[kk][0] = load_pair(valid_a, id_a, hq_a, e);
-                qf[kk][1] = load_pair(valid_b, id_b, hq_b, e);
-                qf[kk][2] = load_pair(valid_a, id_a, hq_a, e + 8);
-                qf[kk][3] = load_pair(valid_b, id_b, hq_b, e + 8);
-            }
+            // ---- per-fragment prologue ----------------------------------------------------------
+            // All consumer threads rotate the block's query rows for this fragment (16-byte chunks,
+            // every load independent: one memory round trip), round them to the storage type and
+            // stage them in shared memory; each warp then pulls its MMA A-fragments with ldmatrix.
             const int vf = vis[f];
-            lim_a = valid_a ? min(a.loc[(f * a.W + id_a.w) * a.S + id_a.s], vf - 1) + 1 : vf;
-            lim_b = valid_b ? min(a.loc[(f * a.W + id_b.w) * a.S + id_b.s], vf - 1) + 1 : vf;
+            const int loc_a = valid_a ? a.loc[(f * a.W + id_a.w) * a.S + id_a.s] : vf;
+            const int loc_b = valid_b ? a.loc[(f * a.W + id_b.w) * a.S + id_b.s] : vf;
+            if (!consumer_sync()) break;                       // everyone is done with the previous query tile
+            if (warp == 1) HOGATT_TL(1, 20);
+            {
+                constexpr int CPR = HD / 8;                                    // 16-byte chunks per row
+                constexpr int ITEMS = C::RPB * CPR / (C::NCW * 32);            // chunks per thread
+                static_assert(ITEMS * C::NCW * 32 == C::RPB * CPR, "chunks must divide evenly over the consumer threads");
+                const bool chunked = a.cos == nullptr || chunked_rope_ok(a.cos, a.sin, a.R, HD);
+                const int ctid = tid - 32;
+                uint4 val[ITEMS];
+                bool live[ITEMS];
+#pragma unroll
+                for (int k = 0; k < ITEMS; ++k) {              // all loads of all chunks are issued before any is used
+                    const int item = ctid + k * (C::NCW * 32);
+                    const int r = item / CPR, ch = item % CPR;
+                    const int gr = rb * C::RPB + r;
+                    live[k] = gr < a.rows_total;
+                    const RowId id = decode_row(live[k] ? gr : 0, a.G, a.S);
+                    const int hq = hkv * a.G + id.g;
+                    if (a.cos == nullptr) {
+                        val[k] = *reinterpret_cast<const uint4*>(
+                            q + ((size_t)((f * a.W + id.w) * a.Hq + hq) * a.S + id.s) * HD + ch * 8);
+                    } else {
+                        const T* qrow = q + ((size_t)(id.w * a.Hq + hq) * a.S + id.s) * HD;
+                        const size_t tab = ((size_t)(f * a.W + id.w) * a.S + id.s) * a.R;
+                        if (chunked) {
+                            val[k] = rotate_chunk<T>(qrow, a.cos + tab, a.sin + tab, ch, a.R);
+                        } else {
+                            uint32_t* o32 = reinterpret_cast<uint32_t*>(&val[k]);
+#pragma unroll
+                            for (int c = 0; c < 4; ++c)
+                                o32[c] = pack2<T>(rope_channel<T>(qrow, a.cos + tab, a.sin + tab, ch * 8 + 2 * c, a.R),
+                                                  rope_channel<T>(qrow, a.cos + tab, a.sin + tab, ch * 8 + 2 * c + 1, a.R));
+                        }
+                    }
+                }
+#pragma unroll
+                for (int k = 0; k < ITEMS; ++k) {
+                    const int item = ctid + k * (C::NCW * 32);
+                    const int r = item / CPR, ch = item % CPR;
+                    *reinterpret_cast<uint4*>(qtile + r * C::QPITCH + ch * 16) = live[k] ? val[k] : make_uint4(0u, 0u, 0u, 0u);
+                }
+            }
+            if (warp == 1) HOGATT_TL(1, 21);
+            if (!consumer_sync()) break;                       // the query tile is complete
+            if (warp == 1) HOGATT_TL(1, 22);
+            {
+                const uint32_t qaddr = smem_u32(qtile) + (mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * C::QPITCH + (lane >> 4) * 16;
+#pragma unroll
+                for (int kk = 0; kk < C::KSTEPS; ++kk)
+                    ldmatrix_x4(qaddr + kk * 32, qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3]);
+            }
+            lim_a = valid_a ? min(loc_a, vf - 1) + 1 : vf;
+            lim_b = valid_b ? min(loc_b, vf - 1) + 1 : vf;
+            if (want_rq && it == 0)
+                write_rotated_queries<T>(a.q, a.rq, a.cos, a.sin, a.F, a.W, a.Hq, a.S, HD, a.R,
+                                         blockIdx.x * (C::NCW * 32) + tid - 32, gridDim.x * (C::NCW * 32));
+            if (warp == 1) HOGATT_TL(1, 10 + f);
         }
         const int tok0 = (j - pre[f]) * C::TILE;
         const int ntok = min(C::TILE, vis[f] - tok0);
@@ -239,6 +294,7 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
         bool ok = mbar_wait_bounded(full0 + 8 * stage, phase, abort_flag, a.status, STATUS_WAIT_FULL_TIMEOUT);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
+        if (warp == 1) HOGATT_TL(1, 100 + it);
 
         const int i0 = slice * C::NT_S;      // first in-group position of this warp's slice
         if (ntok < C::TILE) {
@@ -339,6 +395,7 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
             }
         }
 
+        if (warp == 1) HOGATT_TL(1, 500 + it);
         // ---- end of this CTA's share of the unit: fold the warps together, leave a partial ----
         const bool last = (j == TH - 1) || (t == t1 - 1);
         bool wrote_scratch = false;
@@ -347,66 +404,70 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
             l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
             l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
             l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+            // Every warp parks its accumulators and statistics in this stage's buffer (it is still
+            // owned by the consumers); then each warp combines, for its m-tile, ITS share of the
+            // output columns over all slices and writes that share of the partial to the workspace.
             float* scratch = reinterpret_cast<float*>(stages + (size_t)stage * C::STAGE_BYTES);
-            bool alive = true;
-            if (C::NSLICE > 1) alive = consumer_sync();      // every warp is done reading this stage's K/V
+            if (!consumer_sync()) break;                      // every warp is done reading this stage's K/V
+            {
+                float* dst = scratch + (size_t)(slice * MT + mt) * C::SLOT_FLOATS;
 #pragma unroll
-            for (int h = C::NSLICE / 2; h >= 1 && alive; h >>= 1) {
-                if (slice >= h && slice < 2 * h) {
-                    const int slot = (slice - h) * MT + mt;
-                    float* dst = scratch + (size_t)slot * C::SLOT_FLOATS;
+                for (int n = 0; n < C::NT_O; ++n)
 #pragma unroll
-                    for (int n = 0; n < C::NT_O; ++n)
-#pragma unroll
-                        for (int c = 0; c < 4; ++c) dst[(n * 4 + c) * 32 + lane] = o[n][c];
-                    *reinterpret_cast<float4*>(stats + (slot * 32 + lane) * 4) = make_float4(m_a, m_b, l_a, l_b);
-                    wrote_scratch = true;
-                }
-                alive = consumer_sync();
-                if (!alive) break;
-                if (slice < h) {
-                    const int slot = slice * MT + mt;
-                    const float* src = scratch + (size_t)slot * C::SLOT_FLOATS;
-                    const float4 st = *reinterpret_cast<const float4*>(stats + (slot * 32 + lane) * 4);
-                    const float na = fmaxf(m_a, st.x), nb = fmaxf(m_b, st.y);
-                    const float ua = (na == -INFINITY) ? 0.f : na, ub = (nb == -INFINITY) ? 0.f : nb;
-                    const float fa = exp2f(m_a - ua), ga = exp2f(st.x - ua);
-                    const float fb = exp2f(m_b - ub), gb = exp2f(st.y - ub);
-                    l_a = l_a * fa + st.z * ga;
-                    l_b = l_b * fb + st.w * gb;
-                    m_a = na;
-                    m_b = nb;
-#pragma unroll
-                    for (int n = 0; n < C::NT_O; ++n) {
-                        o[n][0] = o[n][0] * fa + src[(n * 4 + 0) * 32 + lane] * ga;
-                        o[n][1] = o[n][1] * fa + src[(n * 4 + 1) * 32 + lane] * ga;
-                        o[n][2] = o[n][2] * fb + src[(n * 4 + 2) * 32 + lane] * gb;
-                        o[n][3] = o[n][3] * fb + src[(n * 4 + 3) * 32 + lane] * gb;
-                    }
-                }
-                if (h > 1) alive = consumer_sync();          // scratch is rewritten by the next round
+                    for (int c = 0; c < 4; ++c) dst[(n * 4 + c) * 32 + lane] = o[n][c];
+                *reinterpret_cast<float4*>(stats + ((slice * MT + mt) * 32 + lane) * 4) = make_float4(m_a, m_b, l_a, l_b);
+                wrote_scratch = true;
             }
-            if (!alive) break;
-            if (slice == 0) {
-                int first, count;
-                unit_ctas(u, TH, N, ctas, &first, &count);
-                const size_t slot = (size_t)u * a.parts_per_unit + (blockIdx.x - first);
-                float* wo_a = a.ws_o + (slot * C::RPB + row_a) * HD + qlane * 2;
-                float* wo_b = a.ws_o + (slot * C::RPB + row_b) * HD + qlane * 2;
+            if (!consumer_sync()) break;
+            float fa[C::NSLICE], fb[C::NSLICE];
+            float M_a = -INFINITY, M_b = -INFINITY, L_a = 0.f, L_b = 0.f;
+            {
+                float4 st[C::NSLICE];
 #pragma unroll
-                for (int n = 0; n < C::NT_O; ++n) {
-                    *reinterpret_cast<float2*>(wo_a + n * 8) = make_float2(o[n][0], o[n][1]);
-                    *reinterpret_cast<float2*>(wo_b + n * 8) = make_float2(o[n][2], o[n][3]);
+                for (int sl = 0; sl < C::NSLICE; ++sl) {
+                    st[sl] = *reinterpret_cast<const float4*>(stats + ((sl * MT + mt) * 32 + lane) * 4);
+                    M_a = fmaxf(M_a, st[sl].x);
+                    M_b = fmaxf(M_b, st[sl].y);
                 }
-                if (qlane == 0) {
-                    a.ws_m[slot * C::RPB + row_a] = m_a;
-                    a.ws_m[slot * C::RPB + row_b] = m_b;
-                    a.ws_l[slot * C::RPB + row_a] = l_a;
-                    a.ws_l[slot * C::RPB + row_b] = l_b;
+                const float ua = (M_a == -INFINITY) ? 0.f : M_a, ub = (M_b == -INFINITY) ? 0.f : M_b;
+#pragma unroll
+                for (int sl = 0; sl < C::NSLICE; ++sl) {
+                    fa[sl] = exp2f(st[sl].x - ua);
+                    fb[sl] = exp2f(st[sl].y - ub);
+                    L_a += st[sl].z * fa[sl];
+                    L_b += st[sl].w * fb[sl];
                 }
+            }
+            int first, count;
+            unit_ctas(u, TH, N, ctas, &first, &count);
+            const size_t slot = (size_t)u * a.parts_per_unit + (blockIdx.x - first);
+            constexpr int NSHARE = C::NT_O / C::NSLICE;       // output n-tiles this warp combines
+            float* wo_a = a.ws_o + (slot * C::RPB + row_a) * HD + qlane * 2;
+            float* wo_b = a.ws_o + (slot * C::RPB + row_b) * HD + qlane * 2;
+#pragma unroll
+            for (int nn = 0; nn < NSHARE; ++nn) {
+                const int n = slice * NSHARE + nn;
+                float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int sl = 0; sl < C::NSLICE; ++sl) {
+                    const float* src = scratch + (size_t)(sl * MT + mt) * C::SLOT_FLOATS + (n * 4) * 32 + lane;
+                    acc[0] = fmaf(src[0], fa[sl], acc[0]);
+                    acc[1] = fmaf(src[32], fa[sl], acc[1]);
+                    acc[2] = fmaf(src[64], fb[sl], acc[2]);
+                    acc[3] = fmaf(src[96], fb[sl], acc[3]);
+                }
+                *reinterpret_cast<float2*>(wo_a + n * 8) = make_float2(acc[0], acc[1]);
+                *reinterpret_cast<float2*>(wo_b + n * 8) = make_float2(acc[2], acc[3]);
+            }
+            if (slice == 0 && qlane == 0) {
+                a.ws_m[slot * C::RPB + row_a] = M_a;
+                a.ws_m[slot * C::RPB + row_b] = M_b;
+                a.ws_l[slot * C::RPB + row_a] = L_a;
+                a.ws_l[slot * C::RPB + row_b] = L_b;
             }
         }
 
+        if (warp == 1 && last) HOGATT_TL(1, 900);
         // ---- hand the stage back to the producer ----
         if (wrote_scratch || ntok < C::TILE) fence_proxy_async_smem();
         __syncwarp();
