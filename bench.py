@@ -167,7 +167,7 @@ def run_ours(args):
     full, probs = layer_problems(args.workload, args.layers, rank, world, device)
     whole = wl.baseline_problem(args.workload) if world > 1 else full
     bytes_per_call = whole.algorithmic_bytes()                   # whole job, all ranks
-    calls = [CabiCall(p, device) for p in probs]
+    calls = [CabiCall(p, device, want_rq=not args.no_rq) for p in probs]
     stream = torch.cuda.Stream(device)
 
     gathered = None
@@ -376,6 +376,7 @@ def main():
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-rq", action="store_true", help="do not ask for the rotated-query side output")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     ap.add_argument("--no-isolated", action="store_true", help="skip the isolated cold-call leg (profiling runs)")
     args = ap.parse_args()

@@ -3,6 +3,7 @@
 #include <algorithm>
 #include <atomic>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "hogatt_device.cuh"
@@ -59,6 +60,32 @@ int ensure_smem_limit(Kernel kernel, int dev, size_t bytes, std::atomic<size_t>*
     HOGATT_CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
     granted[dev].store(bytes, std::memory_order_release);
     return HOGATT_OK;
+}
+
+// Launch with the programmatic-stream-serialization attribute: the kernel may be scheduled while its
+// stream predecessor is still running (each of our kernels calls griddepcontrol.wait before it
+// touches global memory).  Off unless HOGATT_PDL=1 is set in the environment when the library is first used.
+bool pdl_enabled() {
+    static const bool on = [] {
+        const char* v = getenv("HOGATT_PDL");
+        return v && v[0] == '1';
+    }();
+    return on;
+}
+
+template <class... KArgs, class... Args>
+cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
@@ -153,8 +180,8 @@ int launch_mma(const KernelArgs& args, int F, int dev, int smem_optin, int grid,
     if (smem > (size_t)smem_optin) return HOGATT_ERR_TOO_MANY_FRAGMENTS;
     int rc = ensure_smem_limit(mma_attention_kernel<T, HD, MT>, dev, smem, granted);
     if (rc != HOGATT_OK) return rc;
-    mma_attention_kernel<T, HD, MT><<<grid, C::THREADS, smem, stream>>>(args, evict_first ? 1 : 0);
-    HOGATT_CUDA_OK(cudaGetLastError());
+    HOGATT_CUDA_OK(launch_kernel(mma_attention_kernel<T, HD, MT>, dim3(grid), dim3(C::THREADS), smem, stream, args,
+                                 evict_first ? 1 : 0));
     return HOGATT_OK;
 }
 
@@ -178,8 +205,7 @@ int launch_fma(const KernelArgs& args, int dev, int smem_optin, int grid, cudaSt
     if (smem > (size_t)smem_optin) return HOGATT_ERR_UNSUPPORTED_HEAD_DIM;
     int rc = ensure_smem_limit(fma_attention_kernel<T, EV>, dev, smem, granted);
     if (rc != HOGATT_OK) return rc;
-    fma_attention_kernel<T, EV><<<grid, kFmaThreads, smem, stream>>>(args);
-    HOGATT_CUDA_OK(cudaGetLastError());
+    HOGATT_CUDA_OK(launch_kernel(fma_attention_kernel<T, EV>, dim3(grid), dim3(kFmaThreads), smem, stream, args));
     return HOGATT_OK;
 }
 
@@ -202,9 +228,11 @@ int launch_all(const KernelArgs& args, const Resolved& r, int dev, int smem_opti
     else
         rc = launch_fma_dims<T>(args, dev, smem_optin, grid, stream);
     if (rc != HOGATT_OK) return rc;
+#ifdef HOGATT_EXPERIMENT
+    if (getenv("HOGATT_SKIP_MERGE")) return HOGATT_OK;
+#endif
     dim3 mgrid((unsigned)r.units, (unsigned)ceil_div(r.rows_per_block, kMergeWarps));
-    merge_kernel<T><<<mgrid, kMergeWarps * 32, 0, stream>>>(args);
-    HOGATT_CUDA_OK(cudaGetLastError());
+    HOGATT_CUDA_OK(launch_kernel(merge_kernel<T>, mgrid, dim3(kMergeWarps * 32), 0, stream, args));
     return HOGATT_OK;
 }
 
@@ -213,8 +241,7 @@ int launch_all<float>(const KernelArgs& args, const Resolved& r, int dev, int sm
     int rc = launch_fma_dims<float>(args, dev, smem_optin, grid, stream);
     if (rc != HOGATT_OK) return rc;
     dim3 mgrid((unsigned)r.units, (unsigned)ceil_div(r.rows_per_block, kMergeWarps));
-    merge_kernel<float><<<mgrid, kMergeWarps * 32, 0, stream>>>(args);
-    HOGATT_CUDA_OK(cudaGetLastError());
+    HOGATT_CUDA_OK(launch_kernel(merge_kernel<float>, mgrid, dim3(kMergeWarps * 32), 0, stream, args));
     return HOGATT_OK;
 }
 

@@ -171,6 +171,13 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
     return true;
 }
 
+// Programmatic dependent launch: a kernel launched with the "programmatic stream serialization"
+// attribute may start while its predecessor in the stream is still running; it must call
+// pdl_wait() before it touches anything the predecessor reads or writes.  pdl_trigger() lets the
+// NEXT kernel in the stream start being scheduled.  Both are no-ops for a normal launch.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // generic-proxy writes -> later async-proxy (bulk copy) writes to the same shared memory
 __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

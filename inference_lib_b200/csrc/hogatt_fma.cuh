@@ -44,6 +44,8 @@ __global__ void __launch_bounds__(kFmaThreads) fma_attention_kernel(const __grid
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
+    pdl_wait();
+    pdl_trigger();
     build_tile_prefix(a, kFmaTile, vis, pre);
     const int TH = pre[a.F];
     const int units = a.row_blocks * a.Hkv;

@@ -17,6 +17,8 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const __grid_co
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int u = blockIdx.x;
     const int rb = u / a.Hkv, hkv = u % a.Hkv;
+    pdl_trigger();       // the next call's attention kernel may queue up behind this grid
+    pdl_wait();          // partials are complete and visible once the attention grid has finished
     const int TH = a.header[0], ctas = a.header[1];
     const int units = a.row_blocks * a.Hkv;
     int first = 0, count = 0;
@@ -31,56 +33,54 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const __grid_co
         T* dst = out + ((size_t)(id.w * a.Hq + hkv * a.G + id.g) * a.S + id.s) * Ev;
         const size_t slot0 = (size_t)u * a.parts_per_unit;
 
-        // statistics of up to 32 partials live one per lane (more are folded in by a strided loop);
-        // the weights are then broadcast by shuffle, so the O loads below do not depend on memory
-        float mp = -INFINITY, lp = 0.f;
-        for (int p = lane; p < count; p += 32) {
-            const float m2 = a.ws_m[(slot0 + p) * RPB + row], l2 = a.ws_l[(slot0 + p) * RPB + row];
-            if (p < 32) { mp = m2; lp = l2; }
-        }
-        float M = mp;
-        for (int p = lane + 32; p < count; p += 32) M = fmaxf(M, a.ws_m[(slot0 + p) * RPB + row]);
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
-        const float wp = (M == -INFINITY) ? 0.f : exp2f(mp - M);      // weight of partial `lane`
-        float den = wp * lp;
-        if (M != -INFINITY)
-            for (int p = lane + 32; p < count; p += 32)
-                den += a.ws_l[(slot0 + p) * RPB + row] * exp2f(a.ws_m[(slot0 + p) * RPB + row] - M);
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
-        const bool blind = !(den > 0.f);
-        const float inv = blind ? 0.f : 1.f / den;
-
+        // Every load of the first kBatch partials -- their statistics (one partial per lane) and the
+        // lane's four output columns of each -- is issued before any of them is used, so the merge of
+        // a row costs one memory round trip; partials beyond kBatch (few units on many SMs) are
+        // folded in by a second, strided pass.
+        constexpr int kBatch = 24;
+        const bool have = lane < count;
+        const float mp = have ? __ldcg(a.ws_m + (slot0 + lane) * RPB + row) : -INFINITY;
+        const float lp = have ? __ldcg(a.ws_l + (slot0 + lane) * RPB + row) : 0.f;
+        const size_t pstride = (size_t)RPB * Ev;
         for (int e0 = 0; e0 < Ev; e0 += 128) {          // uniform trip count: the shuffles need every lane
             const int e = e0 + lane * 4;
             const bool mine = e < Ev;
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
             const float* src = a.ws_o + (slot0 * RPB + row) * Ev + (mine ? e : 0);
-            const size_t pstride = (size_t)RPB * Ev;
-            const int c32 = min(count, 32);
-            for (int p0 = 0; p0 < c32; p0 += 8) {
-                float4 x[8];
+            float4 x[kBatch];
 #pragma unroll
-                for (int k = 0; k < 8; ++k)            // eight independent 16-byte loads in flight
-                    x[k] = (p0 + k < c32) ? *reinterpret_cast<const float4*>(src + (p0 + k) * pstride)
-                                          : make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int k = 0; k < kBatch; ++k)
+                x[k] = (k < count) ? __ldcg(reinterpret_cast<const float4*>(src + k * pstride)) : make_float4(0.f, 0.f, 0.f, 0.f);
+
+            float M = mp;
+            for (int p = lane + 32; p < count; p += 32) M = fmaxf(M, __ldcg(a.ws_m + (slot0 + p) * RPB + row));
 #pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    const float wgt = __shfl_sync(0xffffffffu, wp, (p0 + k) & 31);
-                    acc.x = fmaf(x[k].x, wgt, acc.x);
-                    acc.y = fmaf(x[k].y, wgt, acc.y);
-                    acc.z = fmaf(x[k].z, wgt, acc.z);
-                    acc.w = fmaf(x[k].w, wgt, acc.w);
-                }
+            for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+            const float wp = (M == -INFINITY) ? 0.f : exp2f(mp - M);      // weight of partial `lane`
+            float den = wp * lp;
+            if (M != -INFINITY)
+                for (int p = lane + 32; p < count; p += 32)
+                    den += __ldcg(a.ws_l + (slot0 + p) * RPB + row) * exp2f(__ldcg(a.ws_m + (slot0 + p) * RPB + row) - M);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
+            const bool blind = !(den > 0.f);
+            const float inv = blind ? 0.f : 1.f / den;
+
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int k = 0; k < kBatch; ++k) {
+                const float wgt = __shfl_sync(0xffffffffu, wp, k);
+                acc.x = fmaf(x[k].x, wgt, acc.x);
+                acc.y = fmaf(x[k].y, wgt, acc.y);
+                acc.z = fmaf(x[k].z, wgt, acc.z);
+                acc.w = fmaf(x[k].w, wgt, acc.w);
             }
-            for (int p = 32; p < count; ++p) {
-                const float wgt = blind ? 0.f : exp2f(a.ws_m[(slot0 + p) * RPB + row] - M);
-                const float4 x = *reinterpret_cast<const float4*>(src + p * pstride);
-                acc.x = fmaf(x.x, wgt, acc.x);
-                acc.y = fmaf(x.y, wgt, acc.y);
-                acc.z = fmaf(x.z, wgt, acc.z);
-                acc.w = fmaf(x.w, wgt, acc.w);
+            for (int p = kBatch; p < count; ++p) {
+                const float wgt = blind ? 0.f : exp2f(__ldcg(a.ws_m + (slot0 + p) * RPB + row) - M);
+                const float4 y = __ldcg(reinterpret_cast<const float4*>(src + p * pstride));
+                acc.x = fmaf(y.x, wgt, acc.x);
+                acc.y = fmaf(y.y, wgt, acc.y);
+                acc.z = fmaf(y.z, wgt, acc.z);
+                acc.w = fmaf(y.w, wgt, acc.w);
             }
             if (blind) acc = make_float4(0.f, 0.f, 0.f, 0.f);
             if (mine) {

@@ -94,6 +94,8 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_proxy_async_smem();
     }
+    pdl_wait();          // everything above touched only this CTA's shared memory
+    pdl_trigger();       // the merge kernel may take its place on the SMs now; it waits for this grid itself
     build_tile_prefix(a, C::TILE, vis, pre);     // ends with __syncthreads(): barriers are visible too
     if (warp <= 1) HOGATT_TL(warp, 2);
 
