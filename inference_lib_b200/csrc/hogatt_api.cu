@@ -392,6 +392,19 @@ int hogatt_debug_read_timeline(long long* times /*[2][1024]*/, int* tags /*[2][1
     HOGATT_CUDA_OK(cudaMemcpyFromSymbol(counts, g_timeline_n, sizeof(int) * 2));
     return HOGATT_OK;
 }
+int hogatt_debug_cta_times(unsigned long long* out /*[3][256]*/, unsigned int* sm /*[256]*/) {
+    HOGATT_CUDA_OK(cudaMemcpyFromSymbol(out, g_cta_t, sizeof(unsigned long long) * 768));
+    HOGATT_CUDA_OK(cudaMemcpyFromSymbol(sm, g_cta_sm, sizeof(unsigned int) * 256));
+    return HOGATT_OK;
+}
+int hogatt_debug_spans(unsigned long long* out8, int reset) {
+    HOGATT_CUDA_OK(cudaMemcpyFromSymbol(out8, g_span, sizeof(unsigned long long) * 8));
+    if (reset) {
+        unsigned long long init[8] = {~0ull, 0, ~0ull, 0, ~0ull, 0, ~0ull, 0};
+        HOGATT_CUDA_OK(cudaMemcpyToSymbol(g_span, init, sizeof(init)));
+    }
+    return HOGATT_OK;
+}
 #endif
 
 int hogatt_plan_describe(const hogatt_problem* p, const int32_t* visible_rows, int32_t num_sms, int32_t plan[8]) {

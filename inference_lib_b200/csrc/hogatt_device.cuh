@@ -61,6 +61,16 @@ enum DeviceStatusBits : int {
 __device__ long long g_timeline[2][1024];
 __device__ int g_timeline_tag[2][1024];
 __device__ int g_timeline_n[2];
+__device__ unsigned long long g_cta_t[3][256];   // per CTA: start, first tile consumed, end (globaltimer ns)
+__device__ unsigned int g_cta_sm[256];
+__device__ unsigned long long g_span[8];      // [0] attn first start, [1] attn last end, [2] merge first start, [3] merge last end
+#define HOGATT_SPAN_MIN(i) do { if (threadIdx.x == 0) atomicMin(&g_span[i], global_timer_ns_()); } while (0)
+#define HOGATT_SPAN_MAX(i) do { if (threadIdx.x == 0) atomicMax(&g_span[i], global_timer_ns_()); } while (0)
+__device__ __forceinline__ unsigned long long global_timer_ns_() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
 #define HOGATT_TL_DECL int tlc__ = 0
 #define HOGATT_TL(who, tag)                                                              \
     do {                                                                                 \
@@ -73,6 +83,8 @@ __device__ int g_timeline_n[2];
 #else
 #define HOGATT_TL_DECL
 #define HOGATT_TL(who, tag)
+#define HOGATT_SPAN_MIN(i)
+#define HOGATT_SPAN_MAX(i)
 #endif
 
 // ---------------------------------------------------------------------------------------------

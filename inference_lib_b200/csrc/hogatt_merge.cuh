@@ -17,6 +17,7 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const __grid_co
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int u = blockIdx.x;
     const int rb = u / a.Hkv, hkv = u % a.Hkv;
+    HOGATT_SPAN_MIN(2);
     pdl_trigger();       // the next call's attention kernel may queue up behind this grid
     pdl_wait();          // partials are complete and visible once the attention grid has finished
     const int TH = a.header[0], ctas = a.header[1];
@@ -91,6 +92,7 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const __grid_co
             }
         }
     }
+    HOGATT_SPAN_MAX(3);
 }
 
 // rq[f,w,h,s,:] = rope(q[w,h,s,:], cos[f,w,s,:], sin[f,w,s,:]).

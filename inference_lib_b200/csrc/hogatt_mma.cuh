@@ -81,6 +81,15 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     HOGATT_TL_DECL;
     HOGATT_TL(warp == 0 ? 0 : 1, 1);
+    HOGATT_SPAN_MIN(0);
+#ifdef HOGATT_TIMELINE
+    if (tid == 0) {
+        g_cta_t[0][blockIdx.x] = global_timer_ns_();
+        unsigned int smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        g_cta_sm[blockIdx.x] = smid;
+    }
+#endif
     const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * C::NSTAGE, cbar = full0 + 16 * C::NSTAGE;
     const uint32_t stage0 = smem_u32(stages);
 
@@ -171,6 +180,7 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
                 mbar_wait_bounded(full0 + 8 * (k % C::NSTAGE), (uint32_t)(k / C::NSTAGE) & 1u, abort_flag, a.status,
                                   STATUS_DRAIN_TIMEOUT);
         }
+        HOGATT_SPAN_MAX(1);
         return;
     }
 
@@ -297,6 +307,9 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         if (warp == 1) HOGATT_TL(1, 100 + it);
+#ifdef HOGATT_TIMELINE
+        if (warp == 1 && lane == 0 && it == 0) g_cta_t[1][blockIdx.x] = global_timer_ns_();
+#endif
 
         const int i0 = slice * C::NT_S;      // first in-group position of this warp's slice
         if (ntok < C::TILE) {
@@ -480,6 +493,12 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
             ++u;
         }
     }
+#ifdef HOGATT_TIMELINE
+    if (warp == 1 && lane == 0) {
+        atomicMax(&g_span[1], global_timer_ns_());
+        g_cta_t[2][blockIdx.x] = global_timer_ns_();
+    }
+#endif
 }
 
 }  // namespace hogatt
