@@ -56,7 +56,8 @@ typedef enum hogatt_status {
     HOGATT_ERR_WORKSPACE_TOO_SMALL = -7,
     HOGATT_ERR_CUDA = -8,               /* a CUDA runtime call failed; see hogatt_last_cuda_error() */
     HOGATT_ERR_BAD_KERNEL_CHOICE = -9,
-    HOGATT_ERR_TOO_LARGE = -10
+    HOGATT_ERR_TOO_LARGE = -10,
+    HOGATT_ERR_EXCEEDS_STATIC_SCRATCH = -11  /* hogatt_fused_launch_static: needs more than HOGATT_STATIC_SCRATCH_BYTES */
 } hogatt_status;
 
 /* Which device code runs.  AUTO picks the tensor-core kernel for f16/bf16 with E == Ev in {64, 128}
@@ -139,6 +140,31 @@ int hogatt_sdpa_launch(const hogatt_problem* p, hogatt_stream_t stream);
  * (src/binding.cu:324-340).
  */
 int hogatt_fused_launch(const hogatt_problem* p, hogatt_stream_t stream);
+
+/*
+ * hogatt_fused_launch for callers that cannot hand over scratch memory.  It has no counterpart in
+ * the reference.
+ *
+ * Some hosts of this library are not allowed to allocate device memory at the point where they call
+ * it: a plugin that runs inside another runtime's host callback, a process whose device memory is
+ * owned and budgeted by a separate allocator it cannot reach from C, or a real-time loop where
+ * cudaMalloc's implicit device synchronisation is forbidden.  For them the split-K partial sums live in ONE fixed array inside the library image
+ * (HOGATT_STATIC_SCRATCH_BYTES of device memory on every GPU that loads the library, held until the
+ * process exits) instead of `workspace`; `workspace` and `workspace_bytes` are ignored, everything
+ * else is as for hogatt_fused_launch and the results are identical.
+ *
+ *   - A problem whose scratch need (hogatt_workspace_bytes) exceeds HOGATT_STATIC_SCRATCH_BYTES is
+ *     refused with HOGATT_ERR_EXCEEDS_STATIC_SCRATCH and nothing is launched.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
+ *     that device current); make that first call outside any stream capture.  Later calls only
+ *     enqueue kernels.  No call allocates or frees memory.
+ *   - All calls on a device share the one array, which keeps whatever the last call left in it.  The
+ *     kernels write every word of it before they read it, so nothing has to be cleared between
+ *     calls, but two calls that overlap on the GPU (issued on different streams) race on it:
+ *     serialise them, or give the overlapping ones their own workspace through hogatt_fused_launch.
+ */
+#define HOGATT_STATIC_SCRATCH_BYTES (8u << 20)
+int hogatt_fused_launch_static(const hogatt_problem* p, hogatt_stream_t stream);
 
 /*
  * rq[f,w,h,s,:] = rope(queries[w,h,s,:], cosines[f,w,s,:], sines[f,w,s,:]) with the rotate-half

@@ -18,7 +18,7 @@ KERNEL_AUTO, KERNEL_FMA, KERNEL_MMA = 0, 1, 2
 MAX_FRAGMENTS = 128
 
 EXPORTS = ["hogatt_abi_version", "hogatt_status_string", "hogatt_last_cuda_error", "hogatt_workspace_bytes",
-           "hogatt_sdpa_launch", "hogatt_fused_launch", "hogatt_rope_launch", "hogatt_plan_describe",
+           "hogatt_sdpa_launch", "hogatt_fused_launch", "hogatt_fused_launch_static", "hogatt_rope_launch", "hogatt_plan_describe",
            "hogatt_plan_ranges"]
 
 
@@ -51,7 +51,7 @@ def load() -> C.CDLL:
         lib.hogatt_last_cuda_error.restype = C.c_int
         lib.hogatt_workspace_bytes.restype = C.c_size_t
         lib.hogatt_workspace_bytes.argtypes = [C.POINTER(Problem)]
-        for name in ("hogatt_sdpa_launch", "hogatt_fused_launch"):
+        for name in ("hogatt_sdpa_launch", "hogatt_fused_launch", "hogatt_fused_launch_static"):
             fn = getattr(lib, name)
             fn.restype = C.c_int
             fn.argtypes = [C.POINTER(Problem), C.c_void_p]
@@ -124,6 +124,15 @@ def bind(*, out, queries, locations, keys, values, scale, fragment_lengths=None,
 
 def workspace_bytes(bp: BoundProblem) -> int:
     return int(load().hogatt_workspace_bytes(C.byref(bp.struct)))
+
+
+STATIC_SCRATCH_BYTES = 8 << 20
+
+
+def launch_static(bp: BoundProblem, stream: int = 0) -> int:
+    """``hogatt_fused_launch_static``: like :func:`launch` for a fused problem, but the split-K
+    scratch is the library's own fixed device array, so no workspace has to be bound."""
+    return int(load().hogatt_fused_launch_static(C.byref(bp.struct), C.c_void_p(stream)))
 
 
 def launch(bp: BoundProblem, stream: int = 0) -> int:

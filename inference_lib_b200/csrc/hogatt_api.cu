@@ -314,6 +314,26 @@ int attention_launch(const hogatt_problem* p, bool fused, cudaStream_t stream) {
     return HOGATT_ERR_UNSUPPORTED_DTYPE;
 }
 
+// ---- fixed scratch for hogatt_fused_launch_static ---------------------------------------------------
+// In host code `g_static_scratch` is only a handle for the symbol, not a device address; the address
+// the kernels can use comes from cudaGetSymbolAddress, looked up once per device.
+static __device__ __align__(256) unsigned char g_static_scratch[HOGATT_STATIC_SCRATCH_BYTES];
+std::atomic<void*> g_static_scratch_ptr[kMaxDevices];
+
+int static_scratch_for_current_device(void** out) {
+    int dev = -1;
+    HOGATT_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return HOGATT_ERR_CUDA;
+    void* ptr = g_static_scratch_ptr[dev].load(std::memory_order_acquire);
+    if (ptr == nullptr) {
+        HOGATT_CUDA_OK(cudaGetSymbolAddress(&ptr, g_static_scratch));     // device `dev` is current
+        if (ptr == nullptr) return HOGATT_ERR_CUDA;
+        g_static_scratch_ptr[dev].store(ptr, std::memory_order_release);
+    }
+    *out = ptr;
+    return HOGATT_OK;
+}
+
 }  // namespace
 }  // namespace hogatt
 
@@ -336,6 +356,7 @@ const char* hogatt_status_string(int status) {
         case HOGATT_ERR_CUDA: return "a CUDA runtime call failed (hogatt_last_cuda_error())";
         case HOGATT_ERR_BAD_KERNEL_CHOICE: return "the requested kernel cannot run this dtype / head size";
         case HOGATT_ERR_TOO_LARGE: return "problem too large for 32-bit row indexing";
+        case HOGATT_ERR_EXCEEDS_STATIC_SCRATCH: return "problem needs more scratch than the fixed HOGATT_STATIC_SCRATCH_BYTES array of hogatt_fused_launch_static; use hogatt_fused_launch with a caller workspace";
     }
     return "unknown status";
 }
@@ -356,6 +377,24 @@ int hogatt_sdpa_launch(const hogatt_problem* p, hogatt_stream_t stream) {
 
 int hogatt_fused_launch(const hogatt_problem* p, hogatt_stream_t stream) {
     return attention_launch(p, /*fused=*/true, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int hogatt_fused_launch_static(const hogatt_problem* p, hogatt_stream_t stream) {
+    if (p == nullptr) return HOGATT_ERR_NULL_POINTER;
+    const size_t need = hogatt_workspace_bytes(p);
+    if (need == 0) {                         // let the regular path name what is wrong with the problem
+        Resolved r;
+        const int rc = resolve(p, &r);
+        return rc != HOGATT_OK ? rc : HOGATT_ERR_CUDA;
+    }
+    if (need > (size_t)HOGATT_STATIC_SCRATCH_BYTES) return HOGATT_ERR_EXCEEDS_STATIC_SCRATCH;
+    void* scratch = nullptr;
+    const int rc = static_scratch_for_current_device(&scratch);
+    if (rc != HOGATT_OK) return rc;
+    hogatt_problem q = *p;
+    q.workspace = scratch;
+    q.workspace_bytes = HOGATT_STATIC_SCRATCH_BYTES;
+    return attention_launch(&q, /*fused=*/true, reinterpret_cast<cudaStream_t>(stream));
 }
 
 int hogatt_rope_launch(void* rq, const void* queries, const float* cosines, const float* sines, int32_t F, int32_t W,
