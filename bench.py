@@ -172,13 +172,14 @@ def run_ours(args):
 
     gathered = None
     if dist:
+        from inference_lib_b200 import sharded
         gathered = [torch.empty((world,) + tuple(c.out.shape), dtype=c.out.dtype, device=device) for c in calls]
 
     def step_body(sid):
         for i, c in enumerate(calls):
             c.launch(sid)
-            if dist:
-                dist.all_gather_into_tensor(gathered[i], c.out)
+            if dist:       # every rank ends up with the full [W,Hq,S,Ev] output of the layer
+                sharded.gather_heads(c.out, world, gather_buffer=gathered[i])
 
     launches_per_step = 2 * len(calls)
 
@@ -282,7 +283,7 @@ def measure_e2e(args, p: wl.Problem, device, dist, world):
     dk, dv = [torch.empty_like(t, device=device) for t in hk], [torch.empty_like(t, device=device) for t in hv]
     rq = torch.empty((p.F, p.W, p.Hq, p.S, p.E), dtype=p.dtype, device=device)
     out = torch.empty((p.W, p.Hq, p.S, p.Ev), dtype=p.dtype, device=device)
-    hout = torch.empty(out.shape, dtype=out.dtype).pin_memory()
+    hout = torch.empty((p.W, p.Hq * world, p.S, p.Ev), dtype=out.dtype).pin_memory()
     gathered = torch.empty((world,) + tuple(out.shape), dtype=out.dtype, device=device) if dist else None
     h2d = sum(t.numel() * t.element_size() for t in [hq, hcos, hsin, hloc, hlen] + hk + hv)
     d2h = hout.numel() * hout.element_size()
@@ -291,9 +292,11 @@ def measure_e2e(args, p: wl.Problem, device, dist, world):
         for d, h in zip([dq, dcos, dsin, dloc, dlen] + dk + dv, [hq, hcos, hsin, hloc, hlen] + hk + hv):
             d.copy_(h, non_blocking=True)
         A.hogwild_fused(dq, dloc, dk, dv, p.scale, dlen, dcos, dsin, rotated_queries=rq, out=out)
+        res = out
         if dist:
-            dist.all_gather_into_tensor(gathered, out)
-        hout.copy_(out, non_blocking=True)
+            from inference_lib_b200 import sharded
+            res = sharded.gather_heads(out, world, gather_buffer=gathered)
+        hout.copy_(res, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
     for _ in range(3):
