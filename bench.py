@@ -183,15 +183,29 @@ def run_ours(args):
 
     launches_per_step = 2 * len(calls)
 
-    # the step is launch-bound from Python, so replay it as a CUDA graph (single-GPU; NCCL calls stay eager)
+    def capture(body):
+        """The step is launch-bound from Python, so it is replayed as a CUDA graph (only steps without
+        collectives); falls back to eager launches if capture is refused."""
+        if args.no_graph:
+            return None
+        try:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                body(torch.cuda.current_stream().cuda_stream)
+            return g
+        except Exception as exc:                      # noqa: BLE001
+            if rank == 0:
+                print(f"[bench] graph capture failed, running eagerly: {exc}", file=sys.stderr)
+            torch.cuda.synchronize()
+            return None
+
     graph = None
     with torch.cuda.stream(stream):
         step_body(stream.cuda_stream)
         torch.cuda.synchronize()
-        if not dist and not args.no_graph:
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=stream):
-                step_body(torch.cuda.current_stream().cuda_stream)
+        barrier()
+        # NCCL collectives stay outside graphs: capturing them stalled this benchmark on a 2-GPU box
+        graph = None if dist else capture(step_body)
 
         def step():
             if graph is not None:
@@ -208,9 +222,16 @@ def run_ours(args):
         # attention-only time at N > 1 (no gather), for the split the scaling discussion needs
         secs_attn = None
         if dist:
-            def step_attn():
+            def attn_body(sid):
                 for c in calls:
-                    c.launch(torch.cuda.current_stream().cuda_stream)
+                    c.launch(sid)
+            g_attn = capture(attn_body)
+
+            def step_attn():
+                if g_attn is not None:
+                    g_attn.replay()
+                else:
+                    attn_body(torch.cuda.current_stream().cuda_stream)
             secs_attn = time_steps(step_attn, args.steps, args.warmup, barrier)
 
         # isolated, cold call: one launch between events, L2 flushed by a 256 MiB write before it
