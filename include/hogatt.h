@@ -176,6 +176,57 @@ int hogatt_rope_launch(void* rq, const void* queries, const float* cosines, cons
                        int32_t dtype, hogatt_stream_t stream);
 
 /*
+ * The paged variants.  Worker w's keys/values are one paged sequence: key l lives in block
+ * block_table[w, l / block_size] at row l % block_size of cache[num_blocks, Hkv, block_size, E].
+ * Every fragment index f reads that same sequence with its own (already rotated) query, location
+ * and length -- the addressing of the reference kernels (src/kernels/kernel_v21.cuh:402-411).
+ *   fixed layout  (cu_seqlens_q == NULL): queries [F,W,Hq,S,E], out [W,Hq,S,Ev], locations [F,W,S],
+ *                 fragment_lengths [F]                       -- `hogwild_paged_sdpa`
+ *   packed layout (cu_seqlens_q != NULL): queries [F,total_q,Hq,E], out [total_q,Hq,Ev],
+ *                 locations [F,total_q], fragment_lengths [F,W], cu_seqlens_q [W+1] (device)
+ *                                                            -- `hogwild_varlen_paged_sdpa`
+ * All pointers device.  CUDA-core kernel: any of the three dtypes, E <= 256, Ev in {32,64,128,256}.
+ */
+typedef struct hogatt_paged_problem {
+    int32_t F, W, Hq, Hkv, E, Ev;
+    int32_t S;                     /* fixed layout only */
+    int32_t total_q_tokens;        /* packed layout only */
+    int32_t block_size, max_blocks_per_seq;
+    int32_t dtype;
+    float   scale;
+    void*          out;
+    const void*    queries;
+    const int32_t* locations;
+    const int32_t* fragment_lengths;
+    const void*    key_cache;
+    const void*    value_cache;
+    const int32_t* block_table;    /* [W, max_blocks_per_seq] */
+    const int32_t* cu_seqlens_q;   /* [W+1] or NULL */
+    void*   workspace;             /* >= hogatt_paged_workspace_bytes(), 256-byte aligned */
+    size_t  workspace_bytes;
+} hogatt_paged_problem;
+
+size_t hogatt_paged_workspace_bytes(const hogatt_paged_problem* p);
+
+/*
+ * Replaces v21::hogwild_paged_attention_gpu (src/kernels/kernel_v21.cuh:998-1043, operator
+ * `hogwild_paged_sdpa`, src/binding.cu:110-142) and v21::hogwild_varlen_paged_attention_gpu
+ * (:1045-1086, operator `hogwild_varlen_paged_sdpa`, src/binding.cu:144-181).
+ */
+int hogatt_paged_sdpa_launch(const hogatt_paged_problem* p, hogatt_stream_t stream);
+
+/*
+ * Append S_new new key/value rows per (batch, kv head) to the paged caches at positions
+ * seq_lengths[b] + t.  key_states [B,Hkv,S_new,E], value_states [B,Hkv,S_new,Ev], caches
+ * [num_blocks,Hkv,block_size,E/Ev], block_table [B,max_blocks], seq_lengths [B]; all device.
+ * Replaces copy_to_blocks_kernel (src/cache.cuh:6-49, operator `copy_to_blocks`, src/binding.cu:183-215).
+ */
+int hogatt_copy_to_blocks_launch(const void* key_states, const void* value_states, void* key_cache, void* value_cache,
+                                 const int32_t* block_table, const int32_t* seq_lengths, int32_t B, int32_t Hkv,
+                                 int32_t S_new, int32_t E, int32_t Ev, int32_t block_size, int32_t max_blocks,
+                                 int32_t dtype, hogatt_stream_t stream);
+
+/*
  * Host-only description of how a problem is cut into work for the persistent grid; no GPU needed.
  * `visible_rows[f]` is the number of leading keys of fragment f that some query row can see.
  * Fills: plan[0] = tokens per tile, plan[1] = rows per row block, plan[2] = row blocks,

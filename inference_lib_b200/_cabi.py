@@ -18,7 +18,8 @@ KERNEL_AUTO, KERNEL_FMA, KERNEL_MMA = 0, 1, 2
 MAX_FRAGMENTS = 128
 
 EXPORTS = ["hogatt_abi_version", "hogatt_status_string", "hogatt_last_cuda_error", "hogatt_workspace_bytes",
-           "hogatt_sdpa_launch", "hogatt_fused_launch", "hogatt_fused_launch_static", "hogatt_rope_launch", "hogatt_plan_describe",
+           "hogatt_sdpa_launch", "hogatt_fused_launch", "hogatt_fused_launch_static", "hogatt_rope_launch",
+           "hogatt_paged_workspace_bytes", "hogatt_paged_sdpa_launch", "hogatt_copy_to_blocks_launch", "hogatt_plan_describe",
            "hogatt_plan_ranges"]
 
 
@@ -32,6 +33,17 @@ class Problem(C.Structure):
         ("fragment_rows", C.POINTER(C.c_int32)),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("device_status", C.c_void_p),
         ("kernel", C.c_int32), ("max_ctas", C.c_int32),
+    ]
+
+
+class PagedProblem(C.Structure):
+    _fields_ = [
+        ("F", C.c_int32), ("W", C.c_int32), ("Hq", C.c_int32), ("Hkv", C.c_int32), ("E", C.c_int32), ("Ev", C.c_int32),
+        ("S", C.c_int32), ("total_q_tokens", C.c_int32), ("block_size", C.c_int32), ("max_blocks_per_seq", C.c_int32),
+        ("dtype", C.c_int32), ("scale", C.c_float),
+        ("out", C.c_void_p), ("queries", C.c_void_p), ("locations", C.c_void_p), ("fragment_lengths", C.c_void_p),
+        ("key_cache", C.c_void_p), ("value_cache", C.c_void_p), ("block_table", C.c_void_p), ("cu_seqlens_q", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
     ]
 
 
@@ -57,6 +69,12 @@ def load() -> C.CDLL:
             fn.argtypes = [C.POINTER(Problem), C.c_void_p]
         lib.hogatt_rope_launch.restype = C.c_int
         lib.hogatt_rope_launch.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p] + [C.c_int32] * 7 + [C.c_void_p]
+        lib.hogatt_paged_workspace_bytes.restype = C.c_size_t
+        lib.hogatt_paged_workspace_bytes.argtypes = [C.POINTER(PagedProblem)]
+        lib.hogatt_paged_sdpa_launch.restype = C.c_int
+        lib.hogatt_paged_sdpa_launch.argtypes = [C.POINTER(PagedProblem), C.c_void_p]
+        lib.hogatt_copy_to_blocks_launch.restype = C.c_int
+        lib.hogatt_copy_to_blocks_launch.argtypes = [C.c_void_p] * 6 + [C.c_int32] * 8 + [C.c_void_p]
         lib.hogatt_plan_describe.restype = C.c_int
         lib.hogatt_plan_describe.argtypes = [C.POINTER(Problem), C.POINTER(C.c_int32), C.c_int32, C.POINTER(C.c_int32)]
         lib.hogatt_plan_ranges.restype = C.c_int

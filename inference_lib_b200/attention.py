@@ -66,6 +66,43 @@ def hogwild_rope(queries: torch.Tensor, cosines: torch.Tensor, sines: torch.Tens
     return out
 
 
+def hogwild_paged_sdpa(queries: torch.Tensor, locations: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor,
+                       block_table: torch.Tensor, scale: float, fragment_lengths: torch.Tensor,
+                       out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Paged attention: ``queries [F,W,Hq,S,E]`` (rotated), worker ``w`` reads the paged sequence
+    ``block_table[w]`` of ``key_cache / value_cache [NumBlocks,Hkv,bs,E]``.  The reference registers this
+    operator (``src/binding.cu:368-369``) but ships no Python wrapper for it."""
+    if out is None:
+        out = torch.empty((queries.size(1), queries.size(2), queries.size(3), value_cache.size(3)),
+                          dtype=queries.dtype, device=queries.device)
+    torch.ops.libhogatt.hogwild_paged_sdpa(out, scale, locations, queries.contiguous(), fragment_lengths, key_cache,
+                                           value_cache, block_table)
+    return out
+
+
+def hogwild_varlen_paged_sdpa(queries: torch.Tensor, locations: torch.Tensor, key_cache: torch.Tensor,
+                              value_cache: torch.Tensor, block_table: torch.Tensor, scale: float,
+                              fragment_lengths: torch.Tensor, cu_seqlens_q: torch.Tensor,
+                              cu_seqlens_k: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Packed-query paged attention: ``queries [F,total_q,Hq,E]``, ``locations [F,total_q]``,
+    ``fragment_lengths [F,W]``, ``cu_seqlens_q [W+1]`` (``src/binding.cu:372-374``)."""
+    if out is None:
+        out = torch.empty((queries.size(1), queries.size(2), value_cache.size(3)), dtype=queries.dtype, device=queries.device)
+    if cu_seqlens_k is None:
+        cu_seqlens_k = cu_seqlens_q
+    torch.ops.libhogatt.hogwild_varlen_paged_sdpa(out, scale, locations, queries.contiguous(), fragment_lengths, key_cache,
+                                                  value_cache, block_table, cu_seqlens_q, cu_seqlens_k)
+    return out
+
+
+def copy_to_blocks(key_states: torch.Tensor, value_states: torch.Tensor, key_cache: torch.Tensor, value_cache: torch.Tensor,
+                   block_table: torch.Tensor, seq_lengths: torch.Tensor) -> None:
+    """Append ``key_states / value_states [B,Hkv,S_new,E]`` to the paged caches at ``seq_lengths[b] + t``
+    (``src/binding.cu:370-371``)."""
+    torch.ops.libhogatt.copy_to_blocks(key_states.contiguous(), value_states.contiguous(), key_cache, value_cache,
+                                       block_table, seq_lengths)
+
+
 def rotate_half(x: torch.Tensor) -> torch.Tensor:
     """``attention.py:77-81``."""
     h = x.shape[-1] // 2

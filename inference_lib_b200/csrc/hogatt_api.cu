@@ -10,6 +10,7 @@
 #include "hogatt_fma.cuh"
 #include "hogatt_merge.cuh"
 #include "hogatt_mma.cuh"
+#include "hogatt_paged.cuh"
 
 namespace hogatt {
 namespace {
@@ -314,6 +315,67 @@ int attention_launch(const hogatt_problem* p, bool fused, cudaStream_t stream) {
     return HOGATT_ERR_UNSUPPORTED_DTYPE;
 }
 
+// ---- paged variants ----------------------------------------------------------------------------------
+
+struct PagedPlan {
+    int tokens_per_group, head_blocks, groups_bound, units, splits;
+    size_t o, m, l, total;
+};
+
+int plan_paged(const hogatt_paged_problem* p, int sms, PagedPlan* pl) {
+    if (p == nullptr) return HOGATT_ERR_NULL_POINTER;
+    const bool packed = p->cu_seqlens_q != nullptr;
+    if (p->F <= 0 || p->W <= 0 || p->Hq <= 0 || p->Hkv <= 0 || p->E <= 0 || p->Ev <= 0 || p->block_size <= 0 ||
+        p->max_blocks_per_seq <= 0 || p->Hq % p->Hkv != 0 || (packed ? p->total_q_tokens < 0 : p->S <= 0))
+        return HOGATT_ERR_BAD_SHAPE;
+    if (p->dtype != HOGATT_F32 && p->dtype != HOGATT_F16 && p->dtype != HOGATT_BF16) return HOGATT_ERR_UNSUPPORTED_DTYPE;
+    if (p->F > 4096) return HOGATT_ERR_TOO_MANY_FRAGMENTS;
+    const int vec = 16 / (int)dtype_size(p->dtype);
+    if ((p->Ev != 32 && p->Ev != 64 && p->Ev != 128 && p->Ev != 256) || p->E > 256 || p->E % vec != 0)
+        return HOGATT_ERR_UNSUPPORTED_HEAD_DIM;
+    const int G = p->Hq / p->Hkv;
+    pl->tokens_per_group = G >= 16 ? 1 : 16 / G;
+    pl->head_blocks = (G + 15) / 16;
+    const int64_t groups = packed ? ((int64_t)p->total_q_tokens + pl->tokens_per_group - 1) / pl->tokens_per_group + p->W
+                                  : (int64_t)p->W * ((p->S + pl->tokens_per_group - 1) / pl->tokens_per_group);
+    const int64_t units = groups * pl->head_blocks * p->Hkv;
+    if (units > (1 << 24)) return HOGATT_ERR_TOO_LARGE;
+    pl->groups_bound = (int)groups;
+    pl->units = (int)std::max<int64_t>(units, 1);
+    pl->splits = std::max(1, std::min(32, (2 * sms + pl->units - 1) / pl->units));
+    const size_t slots = (size_t)pl->units * pl->splits * kFmaRows;
+    pl->o = 0;
+    pl->m = pl->o + align_up(slots * p->Ev * sizeof(float), 256);
+    pl->l = pl->m + align_up(slots * sizeof(float), 256);
+    pl->total = pl->l + align_up(slots * sizeof(float), 256);
+    return HOGATT_OK;
+}
+
+template <class T, int EV>
+int launch_paged(const PagedArgs& a, const PagedPlan& pl, int dev, int smem_optin, cudaStream_t stream) {
+    static std::atomic<size_t> granted[kMaxDevices];
+    const size_t smem = paged_smem_bytes(a.E, EV, a.F);
+    if (smem > (size_t)smem_optin) return HOGATT_ERR_TOO_MANY_FRAGMENTS;
+    int rc = ensure_smem_limit(paged_attention_kernel<T, EV>, dev, smem, granted);
+    if (rc != HOGATT_OK) return rc;
+    paged_attention_kernel<T, EV><<<dim3(pl.units, pl.splits), kFmaThreads, smem, stream>>>(a);
+    HOGATT_CUDA_OK(cudaGetLastError());
+    paged_merge_kernel<T><<<pl.units, kMergeWarps * 32, 0, stream>>>(a);
+    HOGATT_CUDA_OK(cudaGetLastError());
+    return HOGATT_OK;
+}
+
+template <class T>
+int launch_paged_dims(const PagedArgs& a, const PagedPlan& pl, int dev, int smem_optin, cudaStream_t stream) {
+    switch (a.Ev) {
+        case 32: return launch_paged<T, 32>(a, pl, dev, smem_optin, stream);
+        case 64: return launch_paged<T, 64>(a, pl, dev, smem_optin, stream);
+        case 128: return launch_paged<T, 128>(a, pl, dev, smem_optin, stream);
+        case 256: return launch_paged<T, 256>(a, pl, dev, smem_optin, stream);
+    }
+    return HOGATT_ERR_UNSUPPORTED_HEAD_DIM;
+}
+
 // ---- fixed scratch for hogatt_fused_launch_static ---------------------------------------------------
 // In host code `g_static_scratch` is only a handle for the symbol, not a device address; the address
 // the kernels can use comes from cudaGetSymbolAddress, looked up once per device.
@@ -395,6 +457,93 @@ int hogatt_fused_launch_static(const hogatt_problem* p, hogatt_stream_t stream) 
     q.workspace = scratch;
     q.workspace_bytes = HOGATT_STATIC_SCRATCH_BYTES;
     return attention_launch(&q, /*fused=*/true, reinterpret_cast<cudaStream_t>(stream));
+}
+
+size_t hogatt_paged_workspace_bytes(const hogatt_paged_problem* p) {
+    int dev, sms, smem_optin;
+    if (current_device_info(&dev, &sms, &smem_optin) != HOGATT_OK) return 0;
+    PagedPlan pl;
+    if (plan_paged(p, sms, &pl) != HOGATT_OK) return 0;
+    return pl.total;
+}
+
+int hogatt_paged_sdpa_launch(const hogatt_paged_problem* p, hogatt_stream_t stream_) {
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    int dev, sms, smem_optin;
+    int rc = current_device_info(&dev, &sms, &smem_optin);
+    if (rc != HOGATT_OK) return rc;
+    PagedPlan pl;
+    rc = plan_paged(p, sms, &pl);
+    if (rc != HOGATT_OK) return rc;
+    if (!p->out || !p->queries || !p->locations || !p->fragment_lengths || !p->key_cache || !p->value_cache ||
+        !p->block_table || !p->workspace)
+        return HOGATT_ERR_NULL_POINTER;
+    if (!aligned16(p->out) || !aligned16(p->queries) || !aligned16(p->key_cache) || !aligned16(p->value_cache) ||
+        ((uintptr_t)p->workspace & 255u))
+        return HOGATT_ERR_MISALIGNED;
+    if (p->workspace_bytes < pl.total) return HOGATT_ERR_WORKSPACE_TOO_SMALL;
+    const bool packed = p->cu_seqlens_q != nullptr;
+    if (packed && p->total_q_tokens == 0) return HOGATT_OK;
+
+    PagedArgs a;
+    memset(&a, 0, sizeof(a));
+    a.F = p->F; a.W = p->W; a.Hq = p->Hq; a.Hkv = p->Hkv; a.G = p->Hq / p->Hkv; a.E = p->E; a.Ev = p->Ev;
+    a.S = p->S; a.total_q = packed ? p->total_q_tokens : p->W * p->S;
+    a.block_size = p->block_size; a.max_blocks = p->max_blocks_per_seq;
+    a.tokens_per_group = pl.tokens_per_group; a.head_blocks = pl.head_blocks; a.groups_bound = pl.groups_bound;
+    a.splits = pl.splits;
+    a.l2scale = p->scale * 1.4426950408889634f;
+    if (packed) {     // q [F,total_q,Hq,E], out [total_q,Hq,Ev], loc [F,total_q], len [F,W]; s is the packed token index
+        a.q_f = (long long)a.total_q * p->Hq * p->E; a.q_w = 0; a.q_s = (long long)p->Hq * p->E; a.q_h = p->E;
+        a.o_w = 0; a.o_s = (long long)p->Hq * p->Ev; a.o_h = p->Ev;
+        a.loc_f = a.total_q; a.loc_w = 0; a.len_f = p->W; a.len_w = 1;
+    } else {          // q [F,W,Hq,S,E], out [W,Hq,S,Ev], loc [F,W,S], len [F]
+        a.q_f = (long long)p->W * p->Hq * p->S * p->E; a.q_w = (long long)p->Hq * p->S * p->E; a.q_s = p->E;
+        a.q_h = (long long)p->S * p->E;
+        a.o_w = (long long)p->Hq * p->S * p->Ev; a.o_s = p->Ev; a.o_h = (long long)p->S * p->Ev;
+        a.loc_f = p->W * p->S; a.loc_w = p->S; a.len_f = 1; a.len_w = 0;
+    }
+    a.out = p->out; a.q = p->queries; a.loc = p->locations; a.flen = p->fragment_lengths;
+    a.kcache = p->key_cache; a.vcache = p->value_cache; a.block_table = p->block_table; a.cu_seqlens = p->cu_seqlens_q;
+    unsigned char* ws = static_cast<unsigned char*>(p->workspace);
+    a.ws_o = reinterpret_cast<float*>(ws + pl.o);
+    a.ws_m = reinterpret_cast<float*>(ws + pl.m);
+    a.ws_l = reinterpret_cast<float*>(ws + pl.l);
+    switch (p->dtype) {
+        case HOGATT_F32: return launch_paged_dims<float>(a, pl, dev, smem_optin, stream);
+        case HOGATT_F16: return launch_paged_dims<__half>(a, pl, dev, smem_optin, stream);
+        case HOGATT_BF16: return launch_paged_dims<__nv_bfloat16>(a, pl, dev, smem_optin, stream);
+    }
+    return HOGATT_ERR_UNSUPPORTED_DTYPE;
+}
+
+int hogatt_copy_to_blocks_launch(const void* key_states, const void* value_states, void* key_cache, void* value_cache,
+                                 const int32_t* block_table, const int32_t* seq_lengths, int32_t B, int32_t Hkv,
+                                 int32_t S_new, int32_t E, int32_t Ev, int32_t block_size, int32_t max_blocks,
+                                 int32_t dtype, hogatt_stream_t stream_) {
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    if (!key_states || !value_states || !key_cache || !value_cache || !block_table || !seq_lengths) return HOGATT_ERR_NULL_POINTER;
+    if (B <= 0 || Hkv <= 0 || S_new < 0 || E <= 0 || Ev <= 0 || block_size <= 0 || max_blocks <= 0) return HOGATT_ERR_BAD_SHAPE;
+    if (dtype != HOGATT_F32 && dtype != HOGATT_F16 && dtype != HOGATT_BF16) return HOGATT_ERR_UNSUPPORTED_DTYPE;
+    const int vec = 16 / (int)dtype_size(dtype);
+    if (E % vec != 0 || Ev % vec != 0) return HOGATT_ERR_UNSUPPORTED_HEAD_DIM;
+    if (!aligned16(key_states) || !aligned16(value_states) || !aligned16(key_cache) || !aligned16(value_cache)) return HOGATT_ERR_MISALIGNED;
+    if (S_new == 0) return HOGATT_OK;
+    const int64_t total = (int64_t)B * Hkv * S_new * ((E + Ev) / vec);
+    const unsigned blocks = (unsigned)std::min<int64_t>((total + 255) / 256, 148 * 8);
+    switch (dtype) {
+        case HOGATT_F32:
+            copy_to_blocks_kernel<float><<<blocks, 256, 0, stream>>>((const float*)key_states, (const float*)value_states, (float*)key_cache, (float*)value_cache, block_table, seq_lengths, B, Hkv, S_new, E, Ev, block_size, max_blocks);
+            break;
+        case HOGATT_F16:
+            copy_to_blocks_kernel<__half><<<blocks, 256, 0, stream>>>((const __half*)key_states, (const __half*)value_states, (__half*)key_cache, (__half*)value_cache, block_table, seq_lengths, B, Hkv, S_new, E, Ev, block_size, max_blocks);
+            break;
+        default:
+            copy_to_blocks_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)key_states, (const __nv_bfloat16*)value_states, (__nv_bfloat16*)key_cache, (__nv_bfloat16*)value_cache, block_table, seq_lengths, B, Hkv, S_new, E, Ev, block_size, max_blocks);
+            break;
+    }
+    HOGATT_CUDA_OK(cudaGetLastError());
+    return HOGATT_OK;
 }
 
 int hogatt_rope_launch(void* rq, const void* queries, const float* cosines, const float* sines, int32_t F, int32_t W,

@@ -24,25 +24,125 @@ __host__ __device__ inline size_t fma_smem_bytes(int E, int Ev, int F) {
     return floats * sizeof(float) + ints * sizeof(int);
 }
 
+// The per-tile arithmetic of the FMA path, shared by the fragment kernel and the paged kernels:
+// 16 query rows (fp32 in shared memory) against up to 32 staged keys/values (fp32 in shared memory).
+// Warp w owns the softmax statistics of rows w and w + 8; every thread owns RPT outputs of one column.
+template <int EV>
+struct FmaCore {
+    static constexpr int TPC = kFmaThreads / EV;      // threads per output column
+    static constexpr int RPT = kFmaRows / TPC;        // rows per thread in the PV step
+    static_assert(TPC >= 1 && RPT >= 1 && RPT * TPC == kFmaRows, "EV must be 32, 64, 128 or 256");
+
+    float *Qs, *Ks, *Vs, *Ps, *alpha_s;
+    int* lim_s;
+    int E, lane, warp, out_e, out_r0;
+    float m0, m1, l0s, l1s;
+    float acc[RPT];
+
+    // carve [16][E] Q, [32][E+1] K, [32][EV] V, [16][32] P, [16] alpha, [16] limits; returns the end
+    __device__ __forceinline__ unsigned char* carve(unsigned char* base, int E_) {
+        E = E_;
+        Qs = reinterpret_cast<float*>(base);
+        Ks = Qs + kFmaRows * E;
+        Vs = Ks + kFmaTile * (E + 1);
+        Ps = Vs + kFmaTile * EV;
+        alpha_s = Ps + kFmaRows * kFmaTile;
+        lim_s = reinterpret_cast<int*>(alpha_s + kFmaRows);
+        lane = threadIdx.x & 31;
+        warp = threadIdx.x >> 5;
+        out_e = threadIdx.x % EV;
+        out_r0 = (threadIdx.x / EV) * RPT;
+        return reinterpret_cast<unsigned char*>(lim_s + kFmaRows);
+    }
+    __device__ __forceinline__ void reset() {
+        m0 = m1 = -INFINITY;
+        l0s = l1s = 0.f;
+#pragma unroll
+        for (int r = 0; r < RPT; ++r) acc[r] = 0.f;
+    }
+    // Keys tok0 .. tok0+ntok-1 are staged (V rows past ntok zeroed) and the CTA has synchronised.
+    // Key `k` is visible to row r iff k < lim_s[r].  Ends before the trailing __syncthreads().
+    __device__ __forceinline__ void compute(int tok0, int ntok, float l2scale) {
+        {
+            float s0 = 0.f, s1 = 0.f;
+            if (lane < ntok) {
+                const float* kr = Ks + lane * (E + 1);
+                const float* qa = Qs + warp * E;
+                const float* qb = Qs + (warp + 8) * E;
+                for (int e = 0; e < E; ++e) {
+                    const float kv = kr[e];
+                    s0 = fmaf(qa[e], kv, s0);
+                    s1 = fmaf(qb[e], kv, s1);
+                }
+            }
+            const int key = tok0 + lane;
+            s0 = (lane < ntok && key < lim_s[warp]) ? s0 * l2scale : -INFINITY;
+            s1 = (lane < ntok && key < lim_s[warp + 8]) ? s1 * l2scale : -INFINITY;
+            float x0 = s0, x1 = s1;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                x0 = fmaxf(x0, __shfl_xor_sync(0xffffffffu, x0, o));
+                x1 = fmaxf(x1, __shfl_xor_sync(0xffffffffu, x1, o));
+            }
+            const float n0 = fmaxf(m0, x0), n1 = fmaxf(m1, x1);
+            const float b0 = (n0 == -INFINITY) ? 0.f : n0, b1 = (n1 == -INFINITY) ? 0.f : n1;
+            const float a0 = exp2f(m0 - b0), a1 = exp2f(m1 - b1);
+            const float p0 = exp2f(s0 - b0), p1 = exp2f(s1 - b1);
+            float y0 = p0, y1 = p1;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                y0 += __shfl_xor_sync(0xffffffffu, y0, o);
+                y1 += __shfl_xor_sync(0xffffffffu, y1, o);
+            }
+            l0s = l0s * a0 + y0;
+            l1s = l1s * a1 + y1;
+            m0 = n0;
+            m1 = n1;
+            Ps[warp * kFmaTile + lane] = p0;
+            Ps[(warp + 8) * kFmaTile + lane] = p1;
+            if (lane == 0) {
+                alpha_s[warp] = a0;
+                alpha_s[warp + 8] = a1;
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int r = 0; r < RPT; ++r) {
+            const int row = out_r0 + r;
+            float v = acc[r] * alpha_s[row];
+            const float* pr = Ps + row * kFmaTile;
+#pragma unroll 8
+            for (int k = 0; k < kFmaTile; ++k) v = fmaf(pr[k], Vs[k * EV + out_e], v);
+            acc[r] = v;
+        }
+    }
+    // unnormalised partial -> workspace slot
+    __device__ __forceinline__ void flush(float* ws_o, float* ws_m, float* ws_l, size_t slot) const {
+#pragma unroll
+        for (int r = 0; r < RPT; ++r) ws_o[(slot * kFmaRows + out_r0 + r) * EV + out_e] = acc[r];
+        if (lane == 0) {
+            ws_m[slot * kFmaRows + warp] = m0;
+            ws_m[slot * kFmaRows + warp + 8] = m1;
+            ws_l[slot * kFmaRows + warp] = l0s;
+            ws_l[slot * kFmaRows + warp + 8] = l1s;
+        }
+    }
+};
+
 template <class T, int EV>
 __global__ void __launch_bounds__(kFmaThreads) fma_attention_kernel(const __grid_constant__ KernelArgs a) {
     constexpr int VEC = 16 / sizeof(T);
-    constexpr int TPC = kFmaThreads / EV;      // threads per output column
-    constexpr int RPT = kFmaRows / TPC;        // rows per thread in the PV step
-    static_assert(TPC >= 1 && RPT >= 1 && RPT * TPC == kFmaRows, "EV must be 32, 64, 128 or 256");
-
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int E = a.E;
-    float* Qs = reinterpret_cast<float*>(smem_raw);            // [16][E]
-    float* Ks = Qs + kFmaRows * E;                              // [32][E+1]
-    float* Vs = Ks + kFmaTile * (E + 1);                        // [32][EV]
-    float* Ps = Vs + kFmaTile * EV;                             // [16][32]
-    float* alpha_s = Ps + kFmaRows * kFmaTile;                  // [16]
-    int* lim_s = reinterpret_cast<int*>(alpha_s + kFmaRows);    // [16]
-    int* vis = lim_s + kFmaRows;                                // [F]
-    int* pre = vis + a.F;                                       // [F+1]
+    FmaCore<EV> core;
+    int* vis = reinterpret_cast<int*>(core.carve(smem_raw, E));  // [F]
+    int* pre = vis + a.F;                                        // [F+1]
+    float* const Qs = core.Qs;
+    float* const Ks = core.Ks;
+    float* const Vs = core.Vs;
+    int* const lim_s = core.lim_s;
 
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int tid = threadIdx.x;
 
     pdl_wait();
     pdl_trigger();
@@ -63,10 +163,7 @@ __global__ void __launch_bounds__(kFmaThreads) fma_attention_kernel(const __grid
     const int64_t t0 = cta_first_tile(blockIdx.x, N, ctas), t1 = cta_first_tile(blockIdx.x + 1, N, ctas);
     const T* __restrict__ q = static_cast<const T*>(a.q);
 
-    // warp `warp` owns the softmax of rows warp and warp + 8; every thread owns RPT x 1 outputs
-    float m0 = -INFINITY, m1 = -INFINITY, l0s = 0.f, l1s = 0.f;
-    float acc[RPT];
-    const int out_e = tid % EV, out_r0 = (tid / EV) * RPT;
+    core.reset();
 
     int64_t u = t0 / TH;
     int j = (int)(t0 - u * TH);
@@ -78,10 +175,7 @@ __global__ void __launch_bounds__(kFmaThreads) fma_attention_kernel(const __grid
             fscan = 0;
             rb = cur_u / a.Hkv;
             hkv = cur_u % a.Hkv;
-            m0 = m1 = -INFINITY;
-            l0s = l1s = 0.f;
-#pragma unroll
-            for (int r = 0; r < RPT; ++r) acc[r] = 0.f;
+            core.reset();
         }
         while (j >= pre[fscan + 1]) ++fscan;
         const int f = fscan;
@@ -145,75 +239,13 @@ __global__ void __launch_bounds__(kFmaThreads) fma_attention_kernel(const __grid
         }
         __syncthreads();
 
-        // ---- scores for (row warp, key lane) and (row warp + 8, key lane); online softmax ----
-        {
-            float s0 = 0.f, s1 = 0.f;
-            if (lane < ntok) {
-                const float* kr = Ks + lane * (E + 1);
-                const float* qa = Qs + warp * E;
-                const float* qb = Qs + (warp + 8) * E;
-                for (int e = 0; e < E; ++e) {
-                    const float kv = kr[e];
-                    s0 = fmaf(qa[e], kv, s0);
-                    s1 = fmaf(qb[e], kv, s1);
-                }
-            }
-            const int key = tok0 + lane;
-            s0 = (lane < ntok && key < lim_s[warp]) ? s0 * a.l2scale : -INFINITY;
-            s1 = (lane < ntok && key < lim_s[warp + 8]) ? s1 * a.l2scale : -INFINITY;
-            float x0 = s0, x1 = s1;
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                x0 = fmaxf(x0, __shfl_xor_sync(0xffffffffu, x0, o));
-                x1 = fmaxf(x1, __shfl_xor_sync(0xffffffffu, x1, o));
-            }
-            const float n0 = fmaxf(m0, x0), n1 = fmaxf(m1, x1);
-            const float b0 = (n0 == -INFINITY) ? 0.f : n0, b1 = (n1 == -INFINITY) ? 0.f : n1;
-            const float a0 = exp2f(m0 - b0), a1 = exp2f(m1 - b1);
-            const float p0 = exp2f(s0 - b0), p1 = exp2f(s1 - b1);
-            float y0 = p0, y1 = p1;
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                y0 += __shfl_xor_sync(0xffffffffu, y0, o);
-                y1 += __shfl_xor_sync(0xffffffffu, y1, o);
-            }
-            l0s = l0s * a0 + y0;
-            l1s = l1s * a1 + y1;
-            m0 = n0;
-            m1 = n1;
-            Ps[warp * kFmaTile + lane] = p0;
-            Ps[(warp + 8) * kFmaTile + lane] = p1;
-            if (lane == 0) {
-                alpha_s[warp] = a0;
-                alpha_s[warp + 8] = a1;
-            }
-        }
-        __syncthreads();
-
-        // ---- weighted sum of values ----
-#pragma unroll
-        for (int r = 0; r < RPT; ++r) {
-            const int row = out_r0 + r;
-            float v = acc[r] * alpha_s[row];
-            const float* pr = Ps + row * kFmaTile;
-#pragma unroll 8
-            for (int k = 0; k < kFmaTile; ++k) v = fmaf(pr[k], Vs[k * EV + out_e], v);
-            acc[r] = v;
-        }
+        core.compute(tok0, ntok, a.l2scale);
 
         // ---- leave a partial result where this CTA's share of the unit ends ----
         if (j == TH - 1 || t == t1 - 1) {
             int first, count;
             unit_ctas(u, TH, N, ctas, &first, &count);
-            const size_t slot = (size_t)u * a.parts_per_unit + (blockIdx.x - first);
-#pragma unroll
-            for (int r = 0; r < RPT; ++r) a.ws_o[(slot * kFmaRows + out_r0 + r) * EV + out_e] = acc[r];
-            if (lane == 0) {
-                a.ws_m[slot * kFmaRows + warp] = m0;
-                a.ws_m[slot * kFmaRows + warp + 8] = m1;
-                a.ws_l[slot * kFmaRows + warp] = l0s;
-                a.ws_l[slot * kFmaRows + warp + 8] = l1s;
-            }
+            core.flush(a.ws_o, a.ws_m, a.ws_l, (size_t)u * a.parts_per_unit + (blockIdx.x - first));
         }
         __syncthreads();   // K/V/P/Q buffers are rewritten by the next tile
         if (++j == TH) {

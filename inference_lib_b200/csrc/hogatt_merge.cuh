@@ -6,12 +6,75 @@ namespace hogatt {
 
 constexpr int kMergeWarps = 4;
 
-// One warp per output row: combine the partial results the attention CTAs left for the row's
-// unit, normalise, round to the storage type.
+// Combine the partial results of one output row (one warp), normalise, round to the storage type.
 //   out = sum_p O_p * 2^(m_p - M) / sum_p l_p * 2^(m_p - M),   M = max_p m_p
-// Rows no key was visible to (every m_p = -inf, or no partial at all) come out as zeros.
+// A row no key was visible to (every m_p = -inf, or no partial at all) comes out as zeros.
+// Partial p of the row lives at ws_o[(slot0 + p) * rpb + row][:], ws_m / ws_l likewise.
 // Same role as hogwild_attention_reduce_kernel (src/kernels/kernel_v21.cuh:605-656); that one
 // folds normalised partials pairwise by their log-sum-exp, here the partials are unnormalised.
+// Every load of the first kBatch partials -- their statistics (one partial per lane) and the lane's
+// four output columns of each -- is issued before any of them is used, so a row costs one memory
+// round trip; partials beyond kBatch (few units on many SMs) are folded in by a strided second pass.
+template <class T>
+__device__ __forceinline__ void merge_partials_row(const float* __restrict__ ws_o, const float* __restrict__ ws_m,
+                                                   const float* __restrict__ ws_l, size_t slot0, int rpb, int Ev,
+                                                   int row, int count, T* __restrict__ dst, int lane) {
+    constexpr int kBatch = 24;
+    const bool have = lane < count;
+    const float mp = have ? __ldcg(ws_m + (slot0 + lane) * rpb + row) : -INFINITY;
+    const float lp = have ? __ldcg(ws_l + (slot0 + lane) * rpb + row) : 0.f;
+    const size_t pstride = (size_t)rpb * Ev;
+    for (int e0 = 0; e0 < Ev; e0 += 128) {          // uniform trip count: the shuffles need every lane
+        const int e = e0 + lane * 4;
+        const bool mine = e < Ev;
+        const float* src = ws_o + (slot0 * rpb + row) * Ev + (mine ? e : 0);
+        float4 x[kBatch];
+#pragma unroll
+        for (int k = 0; k < kBatch; ++k)
+            x[k] = (k < count) ? __ldcg(reinterpret_cast<const float4*>(src + k * pstride)) : make_float4(0.f, 0.f, 0.f, 0.f);
+
+        float M = mp;
+        for (int p = lane + 32; p < count; p += 32) M = fmaxf(M, __ldcg(ws_m + (slot0 + p) * rpb + row));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+        const float wp = (M == -INFINITY) ? 0.f : exp2f(mp - M);      // weight of partial `lane`
+        float den = wp * lp;
+        if (M != -INFINITY)
+            for (int p = lane + 32; p < count; p += 32)
+                den += __ldcg(ws_l + (slot0 + p) * rpb + row) * exp2f(__ldcg(ws_m + (slot0 + p) * rpb + row) - M);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
+        const bool blind = !(den > 0.f);
+        const float inv = blind ? 0.f : 1.f / den;
+
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int k = 0; k < kBatch; ++k) {
+            const float wgt = __shfl_sync(0xffffffffu, wp, k);
+            acc.x = fmaf(x[k].x, wgt, acc.x);
+            acc.y = fmaf(x[k].y, wgt, acc.y);
+            acc.z = fmaf(x[k].z, wgt, acc.z);
+            acc.w = fmaf(x[k].w, wgt, acc.w);
+        }
+        for (int p = kBatch; p < count; ++p) {
+            const float wgt = blind ? 0.f : exp2f(__ldcg(ws_m + (slot0 + p) * rpb + row) - M);
+            const float4 y = __ldcg(reinterpret_cast<const float4*>(src + p * pstride));
+            acc.x = fmaf(y.x, wgt, acc.x);
+            acc.y = fmaf(y.y, wgt, acc.y);
+            acc.z = fmaf(y.z, wgt, acc.z);
+            acc.w = fmaf(y.w, wgt, acc.w);
+        }
+        if (blind) acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (mine) {
+            dst[e + 0] = Scalar<T>::from_float(acc.x * inv);
+            dst[e + 1] = Scalar<T>::from_float(acc.y * inv);
+            dst[e + 2] = Scalar<T>::from_float(acc.z * inv);
+            dst[e + 3] = Scalar<T>::from_float(acc.w * inv);
+        }
+    }
+}
+
+// Split-K merge of the fragment op: grid (units, row groups), one warp per output row.
 template <class T>
 __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const __grid_constant__ KernelArgs a) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -26,71 +89,12 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const __grid_co
     if (TH > 0) unit_ctas(u, TH, (int64_t)units * TH, ctas, &first, &count);
     const int RPB = a.rows_per_block, Ev = a.Ev;
     T* __restrict__ out = static_cast<T*>(a.out);
-
     for (int row = blockIdx.y * kMergeWarps + warp; row < RPB; row += gridDim.y * kMergeWarps) {
         const int gr = rb * RPB + row;
         if (gr >= a.rows_total) continue;
         const RowId id = decode_row(gr, a.G, a.S);
         T* dst = out + ((size_t)(id.w * a.Hq + hkv * a.G + id.g) * a.S + id.s) * Ev;
-        const size_t slot0 = (size_t)u * a.parts_per_unit;
-
-        // Every load of the first kBatch partials -- their statistics (one partial per lane) and the
-        // lane's four output columns of each -- is issued before any of them is used, so the merge of
-        // a row costs one memory round trip; partials beyond kBatch (few units on many SMs) are
-        // folded in by a second, strided pass.
-        constexpr int kBatch = 24;
-        const bool have = lane < count;
-        const float mp = have ? __ldcg(a.ws_m + (slot0 + lane) * RPB + row) : -INFINITY;
-        const float lp = have ? __ldcg(a.ws_l + (slot0 + lane) * RPB + row) : 0.f;
-        const size_t pstride = (size_t)RPB * Ev;
-        for (int e0 = 0; e0 < Ev; e0 += 128) {          // uniform trip count: the shuffles need every lane
-            const int e = e0 + lane * 4;
-            const bool mine = e < Ev;
-            const float* src = a.ws_o + (slot0 * RPB + row) * Ev + (mine ? e : 0);
-            float4 x[kBatch];
-#pragma unroll
-            for (int k = 0; k < kBatch; ++k)
-                x[k] = (k < count) ? __ldcg(reinterpret_cast<const float4*>(src + k * pstride)) : make_float4(0.f, 0.f, 0.f, 0.f);
-
-            float M = mp;
-            for (int p = lane + 32; p < count; p += 32) M = fmaxf(M, __ldcg(a.ws_m + (slot0 + p) * RPB + row));
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
-            const float wp = (M == -INFINITY) ? 0.f : exp2f(mp - M);      // weight of partial `lane`
-            float den = wp * lp;
-            if (M != -INFINITY)
-                for (int p = lane + 32; p < count; p += 32)
-                    den += __ldcg(a.ws_l + (slot0 + p) * RPB + row) * exp2f(__ldcg(a.ws_m + (slot0 + p) * RPB + row) - M);
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
-            const bool blind = !(den > 0.f);
-            const float inv = blind ? 0.f : 1.f / den;
-
-            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-            for (int k = 0; k < kBatch; ++k) {
-                const float wgt = __shfl_sync(0xffffffffu, wp, k);
-                acc.x = fmaf(x[k].x, wgt, acc.x);
-                acc.y = fmaf(x[k].y, wgt, acc.y);
-                acc.z = fmaf(x[k].z, wgt, acc.z);
-                acc.w = fmaf(x[k].w, wgt, acc.w);
-            }
-            for (int p = kBatch; p < count; ++p) {
-                const float wgt = blind ? 0.f : exp2f(__ldcg(a.ws_m + (slot0 + p) * RPB + row) - M);
-                const float4 y = __ldcg(reinterpret_cast<const float4*>(src + p * pstride));
-                acc.x = fmaf(y.x, wgt, acc.x);
-                acc.y = fmaf(y.y, wgt, acc.y);
-                acc.z = fmaf(y.z, wgt, acc.z);
-                acc.w = fmaf(y.w, wgt, acc.w);
-            }
-            if (blind) acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (mine) {
-                dst[e + 0] = Scalar<T>::from_float(acc.x * inv);
-                dst[e + 1] = Scalar<T>::from_float(acc.y * inv);
-                dst[e + 2] = Scalar<T>::from_float(acc.z * inv);
-                dst[e + 3] = Scalar<T>::from_float(acc.w * inv);
-            }
-        }
+        merge_partials_row<T>(a.ws_o, a.ws_m, a.ws_l, (size_t)u * a.parts_per_unit, RPB, Ev, row, count, dst, lane);
     }
     HOGATT_SPAN_MAX(3);
 }

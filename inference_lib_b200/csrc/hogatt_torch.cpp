@@ -191,6 +191,130 @@ void hogwild_fused(at::Tensor& out, at::Tensor& rotated_queries, double scale, c
     run_attention(out, &rotated_queries, scale, locations, queries, fragment_lengths, keys, vals, &cosines, &sines);
 }
 
+// --- paged operators (src/binding.cu:269-322) --------------------------------------------------------
+
+void run_paged(at::Tensor& out, double scale, const at::Tensor& locations, const at::Tensor& queries,
+               const at::Tensor& fragment_lengths, const at::Tensor& key_cache, const at::Tensor& value_cache,
+               const at::Tensor& block_table, const at::Tensor* cu_seqlens_q) {
+    TORCH_CHECK(out.is_cuda(), "libhogatt: tensors must live on a CUDA device");
+    const c10::cuda::CUDAGuard guard(out.device());
+    const bool packed = cu_seqlens_q != nullptr;
+    for (const at::Tensor* t : std::initializer_list<const at::Tensor*>{&out, &locations, &queries, &fragment_lengths, &key_cache, &value_cache, &block_table})
+        TORCH_CHECK(t->is_contiguous() && t->device() == out.device(), "paged attention: tensors must be contiguous and on one device");
+    TORCH_CHECK(locations.scalar_type() == at::kInt && fragment_lengths.scalar_type() == at::kInt &&
+                    block_table.scalar_type() == at::kInt, "locations, fragment_lengths, block_table must be int32");
+    TORCH_CHECK(queries.scalar_type() == out.scalar_type() && key_cache.scalar_type() == out.scalar_type() &&
+                    value_cache.scalar_type() == out.scalar_type(), "queries / caches must have the dtype of output");
+    TORCH_CHECK(key_cache.dim() == 4 && value_cache.dim() == 4 && block_table.dim() == 2, "caches [NumBlocks,Hkv,bs,E], block_table [W,max_blocks]");
+    hogatt_paged_problem p = {};
+    p.F = (int32_t)locations.size(0);
+    p.Hkv = (int32_t)key_cache.size(1);
+    p.block_size = (int32_t)key_cache.size(2);
+    p.max_blocks_per_seq = (int32_t)block_table.size(1);
+    TORCH_CHECK_EQ(value_cache.size(1), key_cache.size(1));
+    TORCH_CHECK_EQ(value_cache.size(2), key_cache.size(2));
+    if (packed) {
+        TORCH_CHECK(out.dim() == 3 && queries.dim() == 4 && locations.dim() == 2 && fragment_lengths.dim() == 2,
+                    "varlen: out [total_q,Hq,Ev], queries [F,total_q,Hq,E], locations [F,total_q], fragment_lengths [F,W]");
+        TORCH_CHECK(cu_seqlens_q->scalar_type() == at::kInt && cu_seqlens_q->is_contiguous() && cu_seqlens_q->dim() == 1);
+        p.W = (int32_t)cu_seqlens_q->size(0) - 1;
+        p.total_q_tokens = (int32_t)out.size(0);
+        p.Hq = (int32_t)out.size(1);
+        p.Ev = (int32_t)out.size(2);
+        p.E = (int32_t)queries.size(3);
+        TORCH_CHECK_EQ(queries.size(0), p.F);
+        TORCH_CHECK_EQ(queries.size(1), p.total_q_tokens);
+        TORCH_CHECK_EQ(queries.size(2), p.Hq);
+        TORCH_CHECK_EQ(locations.size(1), p.total_q_tokens);
+        TORCH_CHECK_EQ(fragment_lengths.size(0), p.F);
+        TORCH_CHECK_EQ(fragment_lengths.size(1), p.W);
+        p.cu_seqlens_q = cu_seqlens_q->const_data_ptr<int>();
+    } else {
+        TORCH_CHECK(out.dim() == 4 && queries.dim() == 5 && locations.dim() == 3 && fragment_lengths.dim() == 1,
+                    "paged: out [W,Hq,S,Ev], queries [F,W,Hq,S,E], locations [F,W,S], fragment_lengths [F]");
+        p.W = (int32_t)out.size(0);
+        p.Hq = (int32_t)out.size(1);
+        p.S = (int32_t)out.size(2);
+        p.Ev = (int32_t)out.size(3);
+        p.E = (int32_t)queries.size(4);
+        TORCH_CHECK_EQ(queries.size(0), p.F);
+        TORCH_CHECK_EQ(queries.size(1), p.W);
+        TORCH_CHECK_EQ(queries.size(2), p.Hq);
+        TORCH_CHECK_EQ(queries.size(3), p.S);
+        TORCH_CHECK_EQ(locations.size(1), p.W);
+        TORCH_CHECK_EQ(locations.size(2), p.S);
+        TORCH_CHECK_EQ(fragment_lengths.size(0), p.F);
+    }
+    TORCH_CHECK_EQ(block_table.size(0), p.W);
+    TORCH_CHECK_EQ(key_cache.size(3), p.E);
+    TORCH_CHECK_EQ(value_cache.size(3), p.Ev);
+    p.dtype = dtype_code(out);
+    p.scale = (float)scale;
+    p.out = out.data_ptr();
+    p.queries = queries.const_data_ptr();
+    p.locations = locations.const_data_ptr<int>();
+    p.fragment_lengths = fragment_lengths.const_data_ptr<int>();
+    p.key_cache = key_cache.const_data_ptr();
+    p.value_cache = value_cache.const_data_ptr();
+    p.block_table = block_table.const_data_ptr<int>();
+    if (packed && p.total_q_tokens == 0) return;
+    const size_t need = hogatt_paged_workspace_bytes(&p);
+    TORCH_CHECK(need > 0, "libhogatt: unsupported paged problem (head sizes ", p.E, "/", p.Ev, ", Hq ", p.Hq, ", Hkv ", p.Hkv, ")");
+    at::Tensor workspace = at::empty({(int64_t)need}, out.options().dtype(at::kByte));
+    p.workspace = workspace.data_ptr();
+    p.workspace_bytes = need;
+    const cudaStream_t stream = c10::cuda::getCurrentCUDAStream();
+    check_status(hogatt_paged_sdpa_launch(&p, reinterpret_cast<hogatt_stream_t>(stream)),
+                 packed ? "hogwild_varlen_paged_sdpa" : "hogwild_paged_sdpa");
+}
+
+void hogwild_paged_attention(at::Tensor& out, double scale, const at::Tensor& locations, const at::Tensor& queries,
+                             const at::Tensor& fragment_lengths, const at::Tensor& key_cache,
+                             const at::Tensor& value_cache, const at::Tensor& block_table) {
+    run_paged(out, scale, locations, queries, fragment_lengths, key_cache, value_cache, block_table, nullptr);
+}
+
+void hogwild_varlen_paged_attention(at::Tensor& out, double scale, const at::Tensor& locations, const at::Tensor& queries,
+                                    const at::Tensor& fragment_lengths, const at::Tensor& key_cache,
+                                    const at::Tensor& value_cache, const at::Tensor& block_table,
+                                    const at::Tensor& cu_seqlens_q, const at::Tensor& cu_seqlens_k) {
+    (void)cu_seqlens_k;      // carried by the reference's Shape but never read by its kernels either
+    run_paged(out, scale, locations, queries, fragment_lengths, key_cache, value_cache, block_table, &cu_seqlens_q);
+}
+
+void copy_to_blocks(const at::Tensor& key_states, const at::Tensor& value_states, at::Tensor& key_cache,
+                    at::Tensor& value_cache, const at::Tensor& block_table, const at::Tensor& seq_lengths) {
+    TORCH_CHECK(key_states.is_cuda(), "libhogatt: tensors must live on a CUDA device");
+    const c10::cuda::CUDAGuard guard(key_states.device());
+    for (const at::Tensor* t : {&key_states, &value_states, &block_table, &seq_lengths})
+        TORCH_CHECK(t->is_contiguous(), "copy_to_blocks: inputs must be contiguous");
+    TORCH_CHECK(key_cache.is_contiguous() && value_cache.is_contiguous(), "copy_to_blocks: caches must be contiguous");
+    TORCH_CHECK(key_states.dim() == 4 && value_states.dim() == 4 && key_cache.dim() == 4 && value_cache.dim() == 4 &&
+                    block_table.dim() == 2 && seq_lengths.dim() == 1, "copy_to_blocks: bad ranks");
+    TORCH_CHECK(block_table.scalar_type() == at::kInt && seq_lengths.scalar_type() == at::kInt, "block_table / seq_lengths must be int32");
+    TORCH_CHECK(value_states.scalar_type() == key_states.scalar_type() && key_cache.scalar_type() == key_states.scalar_type() &&
+                    value_cache.scalar_type() == key_states.scalar_type(), "copy_to_blocks: dtype mismatch");
+    const int B = key_states.size(0), Hkv = key_states.size(1), S_new = key_states.size(2), E = key_states.size(3);
+    const int Ev = value_states.size(3);
+    TORCH_CHECK_EQ(value_states.size(0), B);
+    TORCH_CHECK_EQ(value_states.size(1), Hkv);
+    TORCH_CHECK_EQ(value_states.size(2), S_new);
+    TORCH_CHECK_EQ(key_cache.size(1), Hkv);
+    TORCH_CHECK_EQ(key_cache.size(3), E);
+    TORCH_CHECK_EQ(value_cache.size(1), Hkv);
+    TORCH_CHECK_EQ(value_cache.size(3), Ev);
+    TORCH_CHECK_EQ(value_cache.size(2), key_cache.size(2));
+    TORCH_CHECK_EQ(block_table.size(0), B);
+    TORCH_CHECK_EQ(seq_lengths.size(0), B);
+    const cudaStream_t stream = c10::cuda::getCurrentCUDAStream();
+    check_status(hogatt_copy_to_blocks_launch(key_states.const_data_ptr(), value_states.const_data_ptr(), key_cache.data_ptr(),
+                                              value_cache.data_ptr(), block_table.const_data_ptr<int>(),
+                                              seq_lengths.const_data_ptr<int>(), B, Hkv, S_new, E, Ev, (int)key_cache.size(2),
+                                              (int)block_table.size(1), dtype_code(key_states),
+                                              reinterpret_cast<hogatt_stream_t>(stream)),
+                 "copy_to_blocks");
+}
+
 }  // namespace
 
 extern "C" {
@@ -210,10 +334,19 @@ TORCH_LIBRARY(libhogatt, m) {
     m.def("hogwild_rope(Tensor(a!) output, Tensor queries, Tensor cosines, Tensor sines) -> ()", tags, torch::_RegisterOrVerify::REGISTER);
     m.def("hogwild_fused(Tensor(a!) output, Tensor(b!) rq, float scale, Tensor locations, Tensor queries, "
           "Tensor fragment_lengths, Tensor[] key_fragments, Tensor[] value_fragments, Tensor cosines, Tensor sines) -> ()", tags, torch::_RegisterOrVerify::REGISTER);
+    m.def("hogwild_paged_sdpa(Tensor(a!) output, float scale, Tensor locations, Tensor queries, "
+          "Tensor fragment_lengths, Tensor key_cache, Tensor value_cache, Tensor block_table) -> ()", tags, torch::_RegisterOrVerify::REGISTER);
+    m.def("copy_to_blocks(Tensor key_states, Tensor value_states, Tensor(a!) key_cache, Tensor(b!) value_cache, "
+          "Tensor block_table, Tensor seq_lengths) -> ()", tags, torch::_RegisterOrVerify::REGISTER);
+    m.def("hogwild_varlen_paged_sdpa(Tensor(a!) output, float scale, Tensor locations, Tensor queries, "
+          "Tensor fragment_lengths, Tensor key_cache, Tensor value_cache, Tensor block_table, Tensor cu_seqlens_q, Tensor cu_seqlens_k) -> ()", tags, torch::_RegisterOrVerify::REGISTER);
 }
 
 TORCH_LIBRARY_IMPL(libhogatt, CUDA, m) {
     m.impl("hogwild_sdpa", hogwild_attention);
     m.impl("hogwild_rope", hogwild_rope);
     m.impl("hogwild_fused", hogwild_fused);
+    m.impl("hogwild_paged_sdpa", hogwild_paged_attention);
+    m.impl("copy_to_blocks", copy_to_blocks);
+    m.impl("hogwild_varlen_paged_sdpa", hogwild_varlen_paged_attention);
 }

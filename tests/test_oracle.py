@@ -88,3 +88,27 @@ def test_paged_oracle_equals_fragment_oracle_on_gathered_blocks():
         assert torch.equal(out[w:w + 1], ref)
     # token l of worker w lives in block table[w, l // bs], row l % bs
     assert torch.equal(oracle.gather_pages(kc, table[1], 20)[0, :, 17], kc[7, :, 1])
+
+
+def test_varlen_oracle_equals_fixed_layout_oracle_when_lengths_are_equal():
+    torch.manual_seed(1)
+    W, S, Hq, Hkv, E, bs, F = 2, 3, 4, 2, 64, 8, 2
+    kc, vc = torch.randn(12, Hkv, bs, E), torch.randn(12, Hkv, bs, E)
+    table = torch.tensor([[3, 1, 6, 0, 9], [2, 7, 5, 4, 8]], dtype=torch.int32)
+    lens = torch.tensor([33, 20], dtype=torch.int32)
+    rq = torch.randn(F, W, Hq, S, E)
+    loc = torch.randint(0, 40, (F, W, S), dtype=torch.int32)
+    fixed = oracle.paged_sdpa(rq, loc, lens, kc, vc, table, 0.125)                       # [W,Hq,S,Ev]
+    packed_q = rq.permute(0, 1, 3, 2, 4).reshape(F, W * S, Hq, E)
+    packed = oracle.varlen_paged_sdpa(packed_q, loc.reshape(F, W * S), lens[:, None].expand(F, W).contiguous(), kc, vc,
+                                      table, torch.tensor([0, S, 2 * S], dtype=torch.int32), 0.125)
+    assert torch.allclose(packed.reshape(W, S, Hq, E).permute(0, 2, 1, 3), fixed, atol=1e-6)
+
+
+def test_copy_to_blocks_oracle_addresses():
+    kc, vc = torch.zeros(6, 2, 4, 8), torch.zeros(6, 2, 4, 8)
+    table = torch.tensor([[5, 2, 0], [1, 3, 4]], dtype=torch.int32)
+    ks, vs = torch.ones(2, 2, 3, 8), 2 * torch.ones(2, 2, 3, 8)
+    oracle.copy_to_blocks(ks, vs, kc, vc, table, torch.tensor([3, 0], dtype=torch.int32))
+    assert kc[5, :, 3].eq(1).all() and kc[2, :, 0].eq(1).all() and kc[2, :, 1].eq(1).all() and kc[2, :, 2].eq(0).all()
+    assert vc[1, :, :3].eq(2).all() and vc[1, :, 3].eq(0).all()
