@@ -34,7 +34,10 @@ namespace hogatt {
 
 template <int HD, int MT>
 struct MmaCfg {
-    static constexpr int NCW = (MT == 1) ? 4 : 8;        // consumer warps
+    // consumer warps.  Up to 8 warps per CTA may use 255 registers each; from the 9th on the register
+    // file only gives 168, which spills the accumulators -- so two m-tiles run on 4 warps (two key
+    // slices each) rather than 8.
+    static constexpr int NCW = (MT == 4) ? 8 : 4;
     static constexpr int NSLICE = NCW / MT;              // warps sharing one m-tile, each takes a slice of the keys
     static constexpr int GT = (HD == 128) ? 16 : 32;     // keys per group (one 4 KiB bulk copy)
     static constexpr int TILE = 8 * GT;                  // keys per stage
