@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """Benchmark of the Hogwild! fragmented-KV attention op on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload target|cfg2|cfg3|cfg4] [--impl reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload target|cfg2|cfg3|cfg4|cfg5] [--impl reference]
 
 One *step* is one decode step's worth of attention: ``--layers`` (default 32) calls of the fused
 RoPE + attention op, one per transformer layer, each layer with its own KV fragments.  The layers'
@@ -37,6 +37,10 @@ from inference_lib_b200 import workloads as wl  # noqa: E402
 METRIC = "hogwild attn achieved HBM TB/s (us/call in us_per_call)"
 UNIT = "TB/s"
 NOMINAL_HBM_GBS = 8000.0
+# dram__bytes_read.sum + dram__bytes_write.sum of the attention kernel divided by its algorithmic bytes, from the
+# ncu capture summarised in profiles/mma_attention_kernel_target.md (67.248 MB + 0.62 MB against 67.174 MB).
+# DRAM traffic of this kernel grows in proportion to the keys read, so other shapes are scaled by it.
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.0103
 FALLBACK_HBM_GBS = 6650.0
 
 
@@ -279,7 +283,8 @@ def run_ours(args):
         "clocks": clocks,
         "e2e": e2e,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
-                     "frac": round(achieved / peak, 4), "traffic": None, "peak_source": peak_src,
+                     "frac": round(achieved / peak, 4), "traffic": int(per_gpu_bytes * NCU_TRAFFIC_PER_ALGORITHMIC_BYTE),
+                     "traffic_source": "ncu capture at the target shape, scaled by algorithmic bytes", "peak_source": peak_src,
                      "kernel": "mma_attention_kernel (+ merge_kernel in the same interval)",
                      "bytes_per_launch": int(per_gpu_bytes)},
     }
@@ -396,7 +401,7 @@ def main():
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="target", choices=["target", "cfg2", "cfg3", "cfg4"])
+    ap.add_argument("--workload", default="target", choices=["target", "cfg2", "cfg3", "cfg4", "cfg5"])
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -406,6 +411,9 @@ def main():
     args = ap.parse_args()
     if args.workload == "cfg4":
         args.layers = min(args.layers, 4)          # 570 MB of KV per layer
+    if args.workload == "cfg5":
+        args.layers = min(args.layers, 4)          # the four independent groups of that configuration (105 MB each)
+        args.steps = min(args.steps, 20)
     if args.impl == "reference":
         run_reference(args)
     else:
