@@ -36,6 +36,7 @@ extern "C" {
 
 #define HOGATT_ABI_VERSION 1
 #define HOGATT_MAX_FRAGMENTS 128   /* fragment table travels by value in the kernel arguments */
+#define HOGATT_MAX_PEERS 8         /* GPUs of one node that can share a gathered output */
 
 typedef struct CUstream_st* hogatt_stream_t;   /* == cudaStream_t */
 
@@ -165,6 +166,29 @@ int hogatt_fused_launch(const hogatt_problem* p, hogatt_stream_t stream);
  */
 #define HOGATT_STATIC_SCRATCH_BYTES (8u << 20)
 int hogatt_fused_launch_static(const hogatt_problem* p, hogatt_stream_t stream);
+
+/*
+ * KV-head sharding across the GPUs of one node with the output all-gather fused into the op.
+ * No counterpart in the reference (single device, src/kernels/kernel_v21.cuh:960).
+ *
+ * Every rank calls this with ITS shard as the problem (Hkv/world kv heads, Hq/world query heads; `out` is
+ * ignored) and a table of peer-mapped pointers.  The merge step stores each finished output row straight
+ * into the full-size output [W, world*Hq, S, Ev] of EVERY rank (plain stores over NVLink through the peer
+ * mapping) at this rank's head offset; a one-warp kernel then publishes a per-call count to every peer
+ * and waits, for at most about a second (then: bit 32 in device_status), until all peers have published
+ * theirs.  When the call's work has completed on a rank's stream, that rank's out_full is complete.
+ *   out_full[p], flags[p]: rank p's buffers as mapped into THIS GPU's address space (CUDA IPC / VMM /
+ *       symmetric memory); flags[p] is int32[world + 1], zero-filled once before the first call
+ *       (slot world is rank p's own call counter).
+ *   The caller must not let a rank start call k+1 on an out_full that another rank is still reading
+ *   from call k (alternate two buffers, or synchronise the consumers).
+ */
+typedef struct hogatt_peers {
+    int32_t  world, rank;
+    void*    out_full[HOGATT_MAX_PEERS];
+    int32_t* flags[HOGATT_MAX_PEERS];
+} hogatt_peers;
+int hogatt_fused_launch_gather(const hogatt_problem* p, const hogatt_peers* peers, hogatt_stream_t stream);
 
 /*
  * rq[f,w,h,s,:] = rope(queries[w,h,s,:], cosines[f,w,s,:], sines[f,w,s,:]) with the rotate-half

@@ -18,7 +18,7 @@ KERNEL_AUTO, KERNEL_FMA, KERNEL_MMA = 0, 1, 2
 MAX_FRAGMENTS = 128
 
 EXPORTS = ["hogatt_abi_version", "hogatt_status_string", "hogatt_last_cuda_error", "hogatt_workspace_bytes",
-           "hogatt_sdpa_launch", "hogatt_fused_launch", "hogatt_fused_launch_static", "hogatt_rope_launch",
+           "hogatt_sdpa_launch", "hogatt_fused_launch", "hogatt_fused_launch_static", "hogatt_fused_launch_gather", "hogatt_rope_launch",
            "hogatt_paged_workspace_bytes", "hogatt_paged_sdpa_launch", "hogatt_copy_to_blocks_launch", "hogatt_plan_describe",
            "hogatt_plan_ranges"]
 
@@ -47,6 +47,14 @@ class PagedProblem(C.Structure):
     ]
 
 
+MAX_PEERS = 8
+
+
+class Peers(C.Structure):
+    _fields_ = [("world", C.c_int32), ("rank", C.c_int32), ("out_full", C.c_void_p * MAX_PEERS),
+                ("flags", C.c_void_p * MAX_PEERS)]
+
+
 _lib: Optional[C.CDLL] = None
 
 
@@ -67,6 +75,8 @@ def load() -> C.CDLL:
             fn = getattr(lib, name)
             fn.restype = C.c_int
             fn.argtypes = [C.POINTER(Problem), C.c_void_p]
+        lib.hogatt_fused_launch_gather.restype = C.c_int
+        lib.hogatt_fused_launch_gather.argtypes = [C.POINTER(Problem), C.POINTER(Peers), C.c_void_p]
         lib.hogatt_rope_launch.restype = C.c_int
         lib.hogatt_rope_launch.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p] + [C.c_int32] * 7 + [C.c_void_p]
         lib.hogatt_paged_workspace_bytes.restype = C.c_size_t
@@ -151,6 +161,11 @@ def launch_static(bp: BoundProblem, stream: int = 0) -> int:
     """``hogatt_fused_launch_static``: like :func:`launch` for a fused problem, but the split-K
     scratch is the library's own fixed device array, so no workspace has to be bound."""
     return int(load().hogatt_fused_launch_static(C.byref(bp.struct), C.c_void_p(stream)))
+
+
+def launch_gather(bp: BoundProblem, peers: Peers, stream: int = 0) -> int:
+    """``hogatt_fused_launch_gather``: this rank's shard, output rows stored into every rank's full output."""
+    return int(load().hogatt_fused_launch_gather(C.byref(bp.struct), C.byref(peers), C.c_void_p(stream)))
 
 
 def launch(bp: BoundProblem, stream: int = 0) -> int:

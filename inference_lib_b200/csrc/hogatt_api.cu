@@ -248,13 +248,19 @@ int launch_all<float>(const KernelArgs& args, const Resolved& r, int dev, int sm
 
 bool aligned16(const void* p) { return ((uintptr_t)p & 15u) == 0; }
 
-int attention_launch(const hogatt_problem* p, bool fused, cudaStream_t stream) {
+int attention_launch(const hogatt_problem* p, bool fused, cudaStream_t stream, const hogatt_peers* peers = nullptr) {
     Resolved r;
     int rc = resolve(p, &r);
     if (rc != HOGATT_OK) return rc;
-    if (!p->out || !p->queries || !p->locations || !p->key_fragments || !p->value_fragments || !p->fragment_rows ||
-        !p->workspace)
+    if ((!p->out && !peers) || !p->queries || !p->locations || !p->key_fragments || !p->value_fragments ||
+        !p->fragment_rows || !p->workspace)
         return HOGATT_ERR_NULL_POINTER;
+    if (peers) {
+        if (peers->world < 1 || peers->world > HOGATT_MAX_PEERS || peers->rank < 0 || peers->rank >= peers->world)
+            return HOGATT_ERR_BAD_SHAPE;
+        for (int i = 0; i < peers->world; ++i)
+            if (!peers->out_full[i] || !peers->flags[i]) return HOGATT_ERR_NULL_POINTER;
+    }
     if (fused) {
         if (!p->cosines || !p->sines) return HOGATT_ERR_NULL_POINTER;
         if (p->rotary_dim <= 0 || p->rotary_dim > p->E || (p->rotary_dim & 1)) return HOGATT_ERR_BAD_SHAPE;
@@ -263,7 +269,7 @@ int attention_launch(const hogatt_problem* p, bool fused, cudaStream_t stream) {
     }
     const size_t sz = dtype_size(p->dtype);
     if ((p->E * sz) % 16 != 0 || (p->Ev * sz) % 16 != 0) return HOGATT_ERR_UNSUPPORTED_HEAD_DIM;
-    if (!aligned16(p->out) || !aligned16(p->queries) || !aligned16(p->workspace) || ((uintptr_t)p->workspace & 255u))
+    if ((!peers && !aligned16(p->out)) || !aligned16(p->queries) || !aligned16(p->workspace) || ((uintptr_t)p->workspace & 255u))
         return HOGATT_ERR_MISALIGNED;
     if (p->rq && !aligned16(p->rq)) return HOGATT_ERR_MISALIGNED;
     if (fused && (((uintptr_t)p->cosines & 3u) || ((uintptr_t)p->sines & 3u))) return HOGATT_ERR_MISALIGNED;
@@ -297,6 +303,11 @@ int attention_launch(const hogatt_problem* p, bool fused, cudaStream_t stream) {
     args.ws_m = reinterpret_cast<float*>(ws + w.m);
     args.ws_l = reinterpret_cast<float*>(ws + w.l);
     args.status = p->device_status;
+    if (peers) {
+        args.world = peers->world;
+        args.rank = peers->rank;
+        for (int i = 0; i < peers->world; ++i) args.peer_out[i] = peers->out_full[i];
+    }
     for (int f = 0; f < p->F; ++f) {
         const int rows = p->fragment_rows[f];
         if (rows < 0) return HOGATT_ERR_BAD_SHAPE;
@@ -308,11 +319,18 @@ int attention_launch(const hogatt_problem* p, bool fused, cudaStream_t stream) {
     }
 
     switch (p->dtype) {
-        case HOGATT_F32: return launch_all<float>(args, r, dev, smem_optin, grid, stream);
-        case HOGATT_F16: return launch_all<__half>(args, r, dev, smem_optin, grid, stream);
-        case HOGATT_BF16: return launch_all<__nv_bfloat16>(args, r, dev, smem_optin, grid, stream);
+        case HOGATT_F32: rc = launch_all<float>(args, r, dev, smem_optin, grid, stream); break;
+        case HOGATT_F16: rc = launch_all<__half>(args, r, dev, smem_optin, grid, stream); break;
+        case HOGATT_BF16: rc = launch_all<__nv_bfloat16>(args, r, dev, smem_optin, grid, stream); break;
+        default: return HOGATT_ERR_UNSUPPORTED_DTYPE;
     }
-    return HOGATT_ERR_UNSUPPORTED_DTYPE;
+    if (rc != HOGATT_OK || !peers) return rc;
+    PeerFlags pf;
+    memset(&pf, 0, sizeof(pf));
+    for (int i = 0; i < peers->world; ++i) pf.f[i] = peers->flags[i];
+    gather_signal_kernel<<<1, 32, 0, stream>>>(pf, peers->world, peers->rank, p->device_status);
+    HOGATT_CUDA_OK(cudaGetLastError());
+    return HOGATT_OK;
 }
 
 // ---- paged variants ----------------------------------------------------------------------------------
@@ -544,6 +562,11 @@ int hogatt_copy_to_blocks_launch(const void* key_states, const void* value_state
     }
     HOGATT_CUDA_OK(cudaGetLastError());
     return HOGATT_OK;
+}
+
+int hogatt_fused_launch_gather(const hogatt_problem* p, const hogatt_peers* peers, hogatt_stream_t stream) {
+    if (peers == nullptr) return HOGATT_ERR_NULL_POINTER;
+    return attention_launch(p, /*fused=*/true, reinterpret_cast<cudaStream_t>(stream), peers);
 }
 
 int hogatt_rope_launch(void* rq, const void* queries, const float* cosines, const float* sines, int32_t F, int32_t W,

@@ -45,6 +45,11 @@ struct KernelArgs {
     float* ws_m;           // [units][parts][rows_per_block]   running max (base-2, scaled)
     float* ws_l;           // [units][parts][rows_per_block]   running sum
     int* status;           // optional
+    // Fused output all-gather over peer memory (KV-head sharding): when world > 0 the merge step stores
+    // every finished output row into the full-size output of EVERY rank (plain stores through peer
+    // pointers) at this rank's head offset, instead of into `out`.
+    int world, rank;       // world == 0: no gather
+    void* peer_out[HOGATT_MAX_PEERS];      // [W, world * Hq, S, Ev] on each rank, mapped into this GPU's address space
     FragmentTable ft;
 };
 
@@ -52,7 +57,8 @@ enum DeviceStatusBits : int {
     STATUS_WAIT_FULL_TIMEOUT = 1,     // a consumer gave up waiting for a KV tile
     STATUS_WAIT_EMPTY_TIMEOUT = 2,    // the producer gave up waiting for a free stage
     STATUS_WAIT_SYNC_TIMEOUT = 4,     // consumer warps gave up waiting for each other
-    STATUS_DRAIN_TIMEOUT = 8          // copies still in flight when the CTA wanted to leave
+    STATUS_DRAIN_TIMEOUT = 8,         // copies still in flight when the CTA wanted to leave
+    STATUS_WAIT_PEER_TIMEOUT = 32     // a peer GPU never reported its share of a gathered output
 };
 
 // Optional timeline for kernel tuning (compile with -DHOGATT_TIMELINE=<cta>): lane 0 of two warps of

@@ -18,7 +18,8 @@ constexpr int kMergeWarps = 4;
 template <class T>
 __device__ __forceinline__ void merge_partials_row(const float* __restrict__ ws_o, const float* __restrict__ ws_m,
                                                    const float* __restrict__ ws_l, size_t slot0, int rpb, int Ev,
-                                                   int row, int count, T* __restrict__ dst, int lane) {
+                                                   int row, int count, T* const* bases, int nbases, size_t offset,
+                                                   int lane) {
     constexpr int kBatch = 24;
     const bool have = lane < count;
     const float mp = have ? __ldcg(ws_m + (slot0 + lane) * rpb + row) : -INFINITY;
@@ -66,10 +67,15 @@ __device__ __forceinline__ void merge_partials_row(const float* __restrict__ ws_
         }
         if (blind) acc = make_float4(0.f, 0.f, 0.f, 0.f);
         if (mine) {
-            dst[e + 0] = Scalar<T>::from_float(acc.x * inv);
-            dst[e + 1] = Scalar<T>::from_float(acc.y * inv);
-            dst[e + 2] = Scalar<T>::from_float(acc.z * inv);
-            dst[e + 3] = Scalar<T>::from_float(acc.w * inv);
+            const T r0 = Scalar<T>::from_float(acc.x * inv), r1 = Scalar<T>::from_float(acc.y * inv);
+            const T r2 = Scalar<T>::from_float(acc.z * inv), r3 = Scalar<T>::from_float(acc.w * inv);
+            for (int b = 0; b < nbases; ++b) {          // one destination, or the full-size output of every rank
+                T* dst = bases[b] + offset + e;
+                dst[0] = r0;
+                dst[1] = r1;
+                dst[2] = r2;
+                dst[3] = r3;
+            }
         }
     }
 }
@@ -88,15 +94,53 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const __grid_co
     int first = 0, count = 0;
     if (TH > 0) unit_ctas(u, TH, (int64_t)units * TH, ctas, &first, &count);
     const int RPB = a.rows_per_block, Ev = a.Ev;
-    T* __restrict__ out = static_cast<T*>(a.out);
+    T* const local_out = static_cast<T*>(a.out);
+    T* const* bases = a.world > 0 ? reinterpret_cast<T* const*>(a.peer_out) : &local_out;
+    const int nbases = a.world > 0 ? a.world : 1;
+    const int hq_all = a.world > 0 ? a.world * a.Hq : a.Hq;       // heads of the destination tensor
+    const int hq_off = a.world > 0 ? a.rank * a.Hq : 0;           // where this rank's heads start in it
     for (int row = blockIdx.y * kMergeWarps + warp; row < RPB; row += gridDim.y * kMergeWarps) {
         const int gr = rb * RPB + row;
         if (gr >= a.rows_total) continue;
         const RowId id = decode_row(gr, a.G, a.S);
-        T* dst = out + ((size_t)(id.w * a.Hq + hkv * a.G + id.g) * a.S + id.s) * Ev;
-        merge_partials_row<T>(a.ws_o, a.ws_m, a.ws_l, (size_t)u * a.parts_per_unit, RPB, Ev, row, count, dst, lane);
+        const size_t offset = ((size_t)(id.w * hq_all + hq_off + hkv * a.G + id.g) * a.S + id.s) * Ev;
+        merge_partials_row<T>(a.ws_o, a.ws_m, a.ws_l, (size_t)u * a.parts_per_unit, RPB, Ev, row, count, bases, nbases,
+                              offset, lane);
     }
     HOGATT_SPAN_MAX(3);
+}
+
+// Completion exchange of the fused output all-gather: one warp, lane p talks to rank p.
+//   1. bump this rank's call counter (device memory, so that a replayed CUDA graph still counts);
+//   2. publish the new count into slot `rank` of every peer's flag array (system-scope release: the
+//      merge kernel's peer stores, finished at the kernel boundary before this one, are visible first);
+//   3. wait -- bounded -- until every peer has published at least the same count into OUR flag array.
+// flags layout on every rank: int32[world] flags + int32 counter at index `world`.
+struct PeerFlags {
+    int* f[HOGATT_MAX_PEERS];
+};
+__global__ void __launch_bounds__(32) gather_signal_kernel(const __grid_constant__ PeerFlags flags, int world, int rank,
+                                                           int* status) {
+    const int lane = threadIdx.x;
+    int* mine = flags.f[rank];
+    int epoch = 0;
+    if (lane == 0) epoch = atomicAdd(mine + world, 1) + 1;
+    epoch = __shfl_sync(0xffffffffu, epoch, 0);
+    if (lane < world) {
+        __threadfence_system();
+        asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flags.f[lane] + rank), "r"(epoch) : "memory");
+        const uint64_t t0 = global_timer_ns();
+        while (true) {
+            int seen;
+            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(mine + lane) : "memory");
+            if (seen >= epoch) break;
+            if (global_timer_ns() - t0 > kWaitLimitNs) {
+                if (status) atomicOr(status, STATUS_WAIT_PEER_TIMEOUT);
+                break;
+            }
+            __nanosleep(100);
+        }
+    }
 }
 
 // rq[f,w,h,s,:] = rope(q[w,h,s,:], cos[f,w,s,:], sin[f,w,s,:]).

@@ -195,12 +195,12 @@ __global__ void __launch_bounds__(kMergeWarps * 32) paged_merge_kernel(const __g
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     PagedUnit u;
     if (!locate_paged_unit(a, blockIdx.x, &u)) return;
-    T* __restrict__ out = static_cast<T*>(a.out);
+    T* const out = static_cast<T*>(a.out);
     for (int row = warp; row < kFmaRows; row += kMergeWarps) {
         int s_abs, hq;
         if (!paged_row(a, u, row, &s_abs, &hq)) continue;
-        T* dst = out + u.w * a.o_w + s_abs * a.o_s + hq * a.o_h;
-        merge_partials_row<T>(a.ws_o, a.ws_m, a.ws_l, (size_t)blockIdx.x * a.splits, kFmaRows, a.Ev, row, a.splits, dst, lane);
+        merge_partials_row<T>(a.ws_o, a.ws_m, a.ws_l, (size_t)blockIdx.x * a.splits, kFmaRows, a.Ev, row, a.splits, &out, 1,
+                              (size_t)(u.w * a.o_w + s_abs * a.o_s + hq * a.o_h), lane);
     }
 }
 
