@@ -136,8 +136,15 @@ class CabiCall:
         if rc != 0:
             raise RuntimeError(f"hogatt launch failed: {self._cabi.status_string(rc)}")
 
+    def launch_gather(self, peers, stream: int):
+        rc = self._cabi.launch_gather(self.bp, peers, stream)
+        if rc != 0:
+            raise RuntimeError(f"hogatt gather launch failed: {self._cabi.status_string(rc)}")
+
 
 def time_steps(step_fn, steps: int, warmup: int, barrier):
+    torch.cuda.synchronize()
+    barrier()                     # ranks enter the warm-up together (their kernels wait for each other, bounded)
     for _ in range(warmup):
         step_fn()
     torch.cuda.synchronize()
@@ -168,92 +175,132 @@ def run_ours(args):
 
     from inference_lib_b200 import _build
     _build.build_all()
-    full, probs = layer_problems(args.workload, args.layers, rank, world, device)
-    whole = wl.baseline_problem(args.workload) if world > 1 else full
-    bytes_per_call = whole.algorithmic_bytes()                   # whole job, all ranks
-    calls = [CabiCall(p, device, want_rq=not args.no_rq) for p in probs]
     stream = torch.cuda.Stream(device)
 
-    gathered = None
-    if dist:
-        from inference_lib_b200 import sharded
-        gathered = [torch.empty((world,) + tuple(c.out.shape), dtype=c.out.dtype, device=device) for c in calls]
+    def measure(workload, layers, steps, warmup, primary):
+        """Build `layers` device-resident problems of a workload, time `steps` steps (gather included at
+        N > 1), plus the attention-only leg at N > 1 and, for the primary workload, the isolated cold call."""
+        full, probs = layer_problems(workload, layers, rank, world, device)
+        whole = wl.baseline_problem(workload) if world > 1 else full
+        bytes_per_call = whole.algorithmic_bytes()                   # whole job, all ranks
+        calls = [CabiCall(p, device, want_rq=not args.no_rq) for p in probs]
 
-    def step_body(sid):
-        for i, c in enumerate(calls):
-            c.launch(sid)
-            if dist:       # every rank ends up with the full [W,Hq,S,Ev] output of the layer
-                sharded.gather_heads(c.out, world, gather_buffer=gathered[i])
-
-    launches_per_step = 2 * len(calls)
-
-    def capture(body):
-        """The step is launch-bound from Python, so it is replayed as a CUDA graph (only steps without
-        collectives); falls back to eager launches if capture is refused."""
-        if args.no_graph:
-            return None
-        try:
-            g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g, stream=stream):
-                body(torch.cuda.current_stream().cuda_stream)
-            return g
-        except Exception as exc:                      # noqa: BLE001
-            if rank == 0:
-                print(f"[bench] graph capture failed, running eagerly: {exc}", file=sys.stderr)
-            torch.cuda.synchronize()
-            return None
-
-    graph = None
-    with torch.cuda.stream(stream):
-        step_body(stream.cuda_stream)
-        torch.cuda.synchronize()
-        barrier()
-        # NCCL collectives stay outside graphs: capturing them stalled this benchmark on a 2-GPU box
-        graph = None if dist else capture(step_body)
-
-        def step():
-            if graph is not None:
-                graph.replay()
-            else:
-                step_body(torch.cuda.current_stream().cuda_stream)
-
-        sampler = ClockSampler(local)
-        if rank == 0:
-            sampler.start()
-        secs = time_steps(step, args.steps, args.warmup, barrier)
-        clocks = sampler.stop() if rank == 0 else None
-
-        # attention-only time at N > 1 (no gather), for the split the scaling discussion needs
-        secs_attn = None
+        gathered = peer_out = peer_tables = None
+        fused_gather = bool(dist) and args.gather == "fused"
         if dist:
-            def attn_body(sid):
-                for c in calls:
-                    c.launch(sid)
-            g_attn = capture(attn_body)
+            from inference_lib_b200 import sharded
+            if fused_gather:
+                # one full-size output + flag array per layer in symmetric memory; the merge step of every rank
+                # stores its heads into all ranks' outputs over NVLink, no collective call in the step
+                ok = torch.ones(1, dtype=torch.int32, device=device)
+                try:
+                    peer_out = sharded.PeerOutputs(dist.group.WORLD, world, rank, len(calls),
+                                                   (whole.W, whole.Hq, whole.S, whole.Ev), whole.dtype, device)
+                    peer_tables = [peer_out.peers(i) for i in range(len(calls))]
+                except Exception as exc:                  # noqa: BLE001  (no peer mapping on this box: use NCCL)
+                    print(f"[bench] rank {rank}: symmetric memory unavailable ({exc}); gathering with NCCL", file=sys.stderr)
+                    ok.zero_()
+                dist.all_reduce(ok, op=dist.ReduceOp.MIN)       # all ranks take the same path
+                fused_gather = bool(int(ok.item()))
+            if not fused_gather:
+                gathered = [torch.empty((world,) + tuple(c.out.shape), dtype=c.out.dtype, device=device) for c in calls]
 
-            def step_attn():
-                if g_attn is not None:
-                    g_attn.replay()
+        def step_body(sid):
+            for i, c in enumerate(calls):
+                if fused_gather:
+                    c.launch_gather(peer_tables[i], sid)
                 else:
-                    attn_body(torch.cuda.current_stream().cuda_stream)
-            secs_attn = time_steps(step_attn, args.steps, args.warmup, barrier)
+                    c.launch(sid)
+                    if dist:       # every rank ends up with the full [W,Hq,S,Ev] output of the layer
+                        sharded.gather_heads(c.out, world, gather_buffer=gathered[i])
 
-        # isolated, cold call: one launch between events, L2 flushed by a 256 MiB write before it
-        flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
-        iso = []
-        for i in range(0 if args.no_isolated else 12):
-            flush.fill_(i)
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record(); calls[i % len(calls)].launch(torch.cuda.current_stream().cuda_stream); e1.record()
+        launches_per_step = (3 if fused_gather else 2) * len(calls)
+
+        def capture(body):
+            """The step is launch-bound from Python, so it is replayed as a CUDA graph (only steps without
+            collectives); falls back to eager launches if capture is refused."""
+            if args.no_graph:
+                return None
+            try:
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream):
+                    body(torch.cuda.current_stream().cuda_stream)
+                return g
+            except Exception as exc:                      # noqa: BLE001
+                if rank == 0:
+                    print(f"[bench] graph capture failed, running eagerly: {exc}", file=sys.stderr)
+                torch.cuda.synchronize()
+                return None
+
+        graph = None
+        with torch.cuda.stream(stream):
+            step_body(stream.cuda_stream)
             torch.cuda.synchronize()
-            iso.append(e0.elapsed_time(e1) * 1e3)
-        iso_us = statistics.median(iso[2:]) if iso else float("nan")
+            barrier()
+            # NCCL collectives stay outside graphs: capturing them stalled this benchmark on a 2-GPU box
+            graph = None if (dist and not fused_gather) else capture(step_body)
 
-    t = torch.tensor([secs, secs_attn or 0.0], dtype=torch.float64, device=device)
-    if dist:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    secs, secs_attn = float(t[0]), float(t[1])
-    n_calls = args.steps * len(calls)
+            def step():
+                if graph is not None:
+                    graph.replay()
+                else:
+                    step_body(torch.cuda.current_stream().cuda_stream)
+
+            sampler = ClockSampler(local)
+            if rank == 0 and primary:
+                sampler.start()
+            secs = time_steps(step, steps, warmup, barrier)
+            clocks = sampler.stop() if (rank == 0 and primary) else None
+
+            # attention-only time at N > 1 (no gather), for the split the scaling discussion needs
+            secs_attn = None
+            if dist:
+                def attn_body(sid):
+                    for c in calls:
+                        c.launch(sid)
+                g_attn = capture(attn_body)
+
+                def step_attn():
+                    if g_attn is not None:
+                        g_attn.replay()
+                    else:
+                        attn_body(torch.cuda.current_stream().cuda_stream)
+                secs_attn = time_steps(step_attn, steps, warmup, barrier)
+
+            # isolated, cold call: one launch between events, L2 flushed by a 256 MiB write before it
+            flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+            iso = []
+            for i in range(0 if (args.no_isolated or not primary) else 12):
+                flush.fill_(i)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(); calls[i % len(calls)].launch(torch.cuda.current_stream().cuda_stream); e1.record()
+                torch.cuda.synchronize()
+                iso.append(e0.elapsed_time(e1) * 1e3)
+            iso_us = statistics.median(iso[2:]) if iso else float("nan")
+
+        t = torch.tensor([secs, secs_attn or 0.0], dtype=torch.float64, device=device)
+        if dist:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        res = dict(secs=float(t[0]), secs_attn=float(t[1]) or None, n_calls=steps * len(calls), bytes_per_call=bytes_per_call,
+                   launches_per_step=launches_per_step, graph=graph is not None, fused_gather=fused_gather, iso_us=iso_us,
+                   clocks=clocks, full=full, layers=len(calls), kv_resident=int(sum(p.algorithmic_bytes() for p in probs)))
+        del calls, probs, graph, gathered, peer_out, peer_tables
+        torch.cuda.empty_cache()
+        return res
+
+    m = measure(args.workload, args.layers, args.steps, args.warmup, True)
+    secs, secs_attn, n_calls, bytes_per_call = m["secs"], m["secs_attn"], m["n_calls"], m["bytes_per_call"]
+    full, iso_us, clocks, graph_used, fused_gather = m["full"], m["iso_us"], m["clocks"], m["graph"], m["fused_gather"]
+    launches_per_step = m["launches_per_step"]
+    extra = None
+    if args.workload != "cfg4" and not args.no_extra:
+        # the long-context shape (139,264 keys, 570 MB of KV per call) beside the headline shape: the one whose
+        # per-GPU work stays far above the fixed per-call cost when the kv heads are spread over 8 GPUs
+        x = measure("cfg4", 4, 30, 5, False)
+        extra = {"cfg4": {"us_per_call": round(x["secs"] / x["n_calls"] * 1e6, 3),
+                          "value_TBps": round(x["bytes_per_call"] * x["n_calls"] / x["secs"] / 1e12, 4),
+                          "attention_only_us_per_call": round(x["secs_attn"] / x["n_calls"] * 1e6, 3) if x["secs_attn"] else None,
+                          "layers_per_step": x["layers"], "steps": 30, "bytes_per_call": x["bytes_per_call"]}}
     us_per_call = secs / n_calls * 1e6
     value = bytes_per_call * n_calls / secs / 1e12
 
@@ -272,10 +319,12 @@ def run_ours(args):
         "scaling": "strong", "vs_baseline": None, "dtype": str(full.dtype).replace("torch.", "") + " in, fp32 accumulate",
         "data": "synthetic (seeded N(0,1) q/k/v, keys pre-rotated)",
         "config": {"workload": args.workload, **{k: v for k, v in full.meta.items() if k not in ("seed",)},
-                   "layers_per_step": len(calls), "kv_bytes_resident": int(sum(p.algorithmic_bytes() for p in probs)),
+                   "layers_per_step": m["layers"], "kv_bytes_resident": m["kv_resident"],
                    "l2": "inputs larger than L2 (one distinct KV set per layer); isolated call uses an L2 flush",
-                   "parallelism": f"kv-head shard x{world}" if world > 1 else "single GPU",
-                   "cuda_graph": graph is not None},
+                   "parallelism": (f"kv-head shard x{world}, output all-gather " +
+                                   ("fused into the merge step (peer stores)" if fused_gather else "by NCCL")) if world > 1
+                                  else "single GPU",
+                   "cuda_graph": graph_used},
         "us_per_call": round(us_per_call, 3),
         "us_per_call_isolated_cold": round(iso_us, 3),
         "pct_of_nominal_8TBps": round(100 * value * 1e3 / (NOMINAL_HBM_GBS * world), 2),
@@ -288,6 +337,8 @@ def run_ours(args):
                      "kernel": "mma_attention_kernel (+ merge_kernel in the same interval)",
                      "bytes_per_launch": int(per_gpu_bytes)},
     }
+    if extra:
+        line["other_workloads"] = extra
     if secs_attn:
         line["attention_only_us_per_call"] = round(secs_attn / n_calls * 1e6, 3)
     if world == 1 and not args.no_cpu_baseline:
@@ -404,6 +455,9 @@ def main():
     ap.add_argument("--workload", default="target", choices=["target", "cfg2", "cfg3", "cfg4", "cfg5"])
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="skip the additional long-context (cfg4) measurement")
+    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
+                    help="N > 1: how the per-rank outputs are all-gathered (fused = peer stores from the merge kernel)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-rq", action="store_true", help="do not ask for the rotated-query side output")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
