@@ -3,15 +3,17 @@
 // One persistent CTA per SM walks a contiguous range of KV tiles (see hogatt_plan.h).
 //   * warp 0 is the producer: it streams K and V tiles global -> shared with 1-D bulk async
 //     copies (TMA engine) into a ring of NSTAGE stages, completion counted on mbarriers.  A tile
-//     is up to 64 (head size 128) or 128 (head size 64) consecutive keys of one fragment and one
+//     is a run of consecutive keys of one fragment and one
 //     kv head, which is one contiguous byte run because fragments are [Hkv, rows, E] row-major.
+//     (A tile is 128 keys at head size 128 and 256 keys at head size 64: 64 KiB per stage, 3 stages.)
 //   * consumer warps each keep 16 query rows (one MMA m-tile) of the kv head resident -- ALL
 //     workers and GQA heads of the head share every K/V tile, so KV is read from HBM once per
 //     call -- and take a slice of every tile: S = Q K^T and O += P V with mma.sync m16n8k16,
 //     fp32 accumulate, online softmax in base 2 in registers.  The per-fragment query RoPE is
-//     done in the prologue of each fragment: the warp builds its MMA A-fragments straight from
-//     the un-rotated query and the cos/sin rows (rounded to the storage type first, as the
-//     reference's rope kernel does before attention reads them, src/rope.cuh:43-45).
+//     done in the prologue of each fragment: all consumer threads rotate 16-byte chunks of the
+//     un-rotated query with the cos/sin rows (rounded to the storage type first, as the
+//     reference's rope kernel does before attention reads them, src/rope.cuh:43-45), stage them in
+//     shared memory, and each warp pulls its MMA A-fragments from there with ldmatrix.
 //   * where the CTA's share of a (kv head, row block) unit ends, the warps fold their private
 //     (O, max, sum) together through shared memory and leave one partial in the workspace.
 //
@@ -20,8 +22,8 @@
 // keys but over the 8 groups at a fixed position i inside the group: key = g * GT + i.  The 16
 // bytes of padding per group rotate the bank of equal chunks by one 16-byte unit per group, so
 // the 8 row addresses of every ldmatrix phase fall into 8 different bank groups: no bank
-// conflicts although the bulk copies land rows unswizzled.  A fragment tile is 8 bulk copies of
-// 2 KiB for K and 8 for V.
+// conflicts although the bulk copies land rows unswizzled.  A tile is 8 bulk copies of 4 KiB for K
+// and 8 for V (issuing a copy costs the producer ~55 ns whatever its size, so copies are made large).
 //
 // The reference kernel (src/kernels/kernel_v21.cuh:28-316) assigns one (kv head, worker, token,
 // split) to a CTA, keeps the GQA heads' queries and accumulators in registers/local memory,
