@@ -103,6 +103,9 @@ def layer_problems(name: str, layers: int, rank: int, world: int, device):
     reuse its queries and metadata with their own KV memory (layer i's KV = layer 0's values rolled
     by i rows), so the layers occupy distinct HBM without spending minutes in the CPU generator."""
     base = wl.baseline_problem(name)
+    if LENGTH_SCALE != 1.0:       # context-length sweeps: same heads and workers, every fragment scaled
+        lengths = [max(base.S, int(l * LENGTH_SCALE)) for l in wl.BASELINE_CONFIGS[name]["lengths"]]
+        base = wl.baseline_problem(name, lengths=lengths)
     if world > 1:
         base = base.shard(rank, world)
     d0 = base.to(device)
@@ -114,6 +117,10 @@ def layer_problems(name: str, layers: int, rank: int, world: int, device):
     return base, probs
 
 
+KERNEL_CHOICE = 0          # hogatt_kernel_choice passed to every call (--kernel)
+LENGTH_SCALE = 1.0         # --scale-lengths
+
+
 class CabiCall:
     """One pre-bound C-ABI call (pointers fixed, so the step can be captured into a CUDA graph)."""
 
@@ -123,7 +130,10 @@ class CabiCall:
         self.out = torch.empty((p.W, p.Hq, p.S, p.Ev), dtype=p.dtype, device=device)
         self.rq = torch.empty((p.F, p.W, p.Hq, p.S, p.E), dtype=p.dtype, device=device) if want_rq else None
         self.bp = _cabi.bind(out=self.out, queries=p.queries, locations=p.locations, keys=p.keys, values=p.values,
-                             scale=p.scale, fragment_lengths=p.fragment_lengths, cos=p.cos, sin=p.sin, rq=self.rq)
+                             scale=p.scale, fragment_lengths=p.fragment_lengths, cos=p.cos, sin=p.sin, rq=self.rq,
+                             kernel=KERNEL_CHOICE)
+        # 1 when the attention kernel merges its split-K partials itself, 2 when merge_kernel follows
+        self.kernels_per_call = _cabi.launch_shape(self.bp)["kernels_per_call"]
         need = _cabi.workspace_bytes(self.bp)
         if need == 0:
             raise RuntimeError("libhogatt_b200 refused the workload")
@@ -214,7 +224,7 @@ def run_ours(args):
                     if dist:       # every rank ends up with the full [W,Hq,S,Ev] output of the layer
                         sharded.gather_heads(c.out, world, gather_buffer=gathered[i])
 
-        launches_per_step = (3 if fused_gather else 2) * len(calls)
+        launches_per_step = sum(c.kernels_per_call + (1 if fused_gather else 0) for c in calls)
 
         def capture(body):
             """The step is launch-bound from Python, so it is replayed as a CUDA graph (only steps without
@@ -458,11 +468,18 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="skip the additional long-context (cfg4) measurement")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="N > 1: how the per-rank outputs are all-gathered (fused = peer stores from the merge kernel)")
+    ap.add_argument("--kernel", default="auto", choices=["auto", "persistent", "cluster"],
+                    help="launch shape of the tensor-core kernel (auto = the library's own choice)")
+    ap.add_argument("--scale-lengths", type=float, default=1.0,
+                    help="multiply every fragment length of the workload (context-length sweeps; not the headline number)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-rq", action="store_true", help="do not ask for the rotated-query side output")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     ap.add_argument("--no-isolated", action="store_true", help="skip the isolated cold-call leg (profiling runs)")
     args = ap.parse_args()
+    global KERNEL_CHOICE, LENGTH_SCALE
+    LENGTH_SCALE = args.scale_lengths
+    KERNEL_CHOICE = {"auto": 0, "persistent": 2, "cluster": 3}[args.kernel]
     if args.workload == "cfg4":
         args.layers = min(args.layers, 4)          # 570 MB of KV per layer
     if args.workload == "cfg5":

@@ -62,11 +62,20 @@ typedef enum hogatt_status {
 } hogatt_status;
 
 /* Which device code runs.  AUTO picks the tensor-core kernel for f16/bf16 with E == Ev in {64, 128}
- * and the FMA kernel for everything else (fp32, other head sizes). */
+ * and the FMA kernel for everything else (fp32, other head sizes).  The tensor-core kernel has two
+ * launch shapes: a persistent grid (one CTA per SM over balanced tile ranges, partial results in the
+ * workspace, a merge kernel after it) and a thread-block-cluster grid (one cluster per kv head and row
+ * block, partial results merged through distributed shared memory inside the same kernel, nothing
+ * written to the workspace).  AUTO takes the cluster shape for short contexts (below about 40 MB of K/V
+ * per call on a B200), where the second launch and the workspace round trip dominate, and the
+ * persistent grid otherwise; MMA forces the persistent grid, MMA_CLUSTER forces the cluster shape
+ * (HOGATT_ERR_BAD_KERNEL_CHOICE when there are more units than half the SMs, or the device cannot
+ * hold one cluster per unit at once).  hogatt_launch_shape() tells which one a problem gets. */
 typedef enum hogatt_kernel_choice {
     HOGATT_KERNEL_AUTO = 0,
     HOGATT_KERNEL_FMA = 1,
-    HOGATT_KERNEL_MMA = 2
+    HOGATT_KERNEL_MMA = 2,
+    HOGATT_KERNEL_MMA_CLUSTER = 3
 } hogatt_kernel_choice;
 
 /*
@@ -254,13 +263,25 @@ int hogatt_copy_to_blocks_launch(const void* key_states, const void* value_state
  * Host-only description of how a problem is cut into work for the persistent grid; no GPU needed.
  * `visible_rows[f]` is the number of leading keys of fragment f that some query row can see.
  * Fills: plan[0] = tokens per tile, plan[1] = rows per row block, plan[2] = row blocks,
- * plan[3] = tiles per (row block, kv head) unit, plan[4] = units, plan[5] = CTAs that get work,
- * plan[6] = partial-result slots per unit, plan[7] = kernel chosen (hogatt_kernel_choice).
+ * plan[3] = tiles per (row block, kv head) unit, plan[4] = units, plan[5] = CTAs that get work
+ * (cluster shape: units x CTAs per cluster), plan[6] = partial-result slots per unit (cluster shape:
+ * CTAs per cluster), plan[7] = kernel chosen (hogatt_kernel_choice; HOGATT_KERNEL_MMA_CLUSTER when
+ * the cluster shape would run, taking visible_rows as the fragments' row counts).
  * Used by the tests of the split-K decomposition; has no reference counterpart (the reference
  * derives `splits` inline, src/kernels/kernel_v21.cuh:957-964).
  */
 int hogatt_plan_describe(const hogatt_problem* p, const int32_t* visible_rows, int32_t num_sms,
                          int32_t plan[8]);
+
+/*
+ * What one hogatt_sdpa_launch / hogatt_fused_launch of this problem enqueues on the current device
+ * (dims, dtype, kernel, max_ctas and fragment_rows are read): shape[0] = device code
+ * (hogatt_kernel_choice, never AUTO), shape[1] = CTAs of the attention grid, shape[2] = CTAs per
+ * cluster (0: no clusters; an upper bound, a forced cluster launch shrinks it until all clusters are
+ * resident), shape[3] = kernels per call (1 when the attention kernel merges by itself, 2 with the
+ * merge kernel).  No reference counterpart.
+ */
+int hogatt_launch_shape(const hogatt_problem* p, int32_t shape[4]);
 
 /*
  * For the decomposition above: the half-open range of global tile indices CTA `cta` walks

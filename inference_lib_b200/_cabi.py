@@ -14,13 +14,13 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG, "libhogatt_b200.so")
 
 F32, F16, BF16 = 0, 1, 2
-KERNEL_AUTO, KERNEL_FMA, KERNEL_MMA = 0, 1, 2
+KERNEL_AUTO, KERNEL_FMA, KERNEL_MMA, KERNEL_MMA_CLUSTER = 0, 1, 2, 3
 MAX_FRAGMENTS = 128
 
 EXPORTS = ["hogatt_abi_version", "hogatt_status_string", "hogatt_last_cuda_error", "hogatt_workspace_bytes",
            "hogatt_sdpa_launch", "hogatt_fused_launch", "hogatt_fused_launch_static", "hogatt_fused_launch_gather", "hogatt_rope_launch",
            "hogatt_paged_workspace_bytes", "hogatt_paged_sdpa_launch", "hogatt_copy_to_blocks_launch", "hogatt_plan_describe",
-           "hogatt_plan_ranges"]
+           "hogatt_plan_ranges", "hogatt_launch_shape"]
 
 
 class Problem(C.Structure):
@@ -85,6 +85,8 @@ def load() -> C.CDLL:
         lib.hogatt_paged_sdpa_launch.argtypes = [C.POINTER(PagedProblem), C.c_void_p]
         lib.hogatt_copy_to_blocks_launch.restype = C.c_int
         lib.hogatt_copy_to_blocks_launch.argtypes = [C.c_void_p] * 6 + [C.c_int32] * 8 + [C.c_void_p]
+        lib.hogatt_launch_shape.restype = C.c_int
+        lib.hogatt_launch_shape.argtypes = [C.POINTER(Problem), C.POINTER(C.c_int32)]
         lib.hogatt_plan_describe.restype = C.c_int
         lib.hogatt_plan_describe.argtypes = [C.POINTER(Problem), C.POINTER(C.c_int32), C.c_int32, C.POINTER(C.c_int32)]
         lib.hogatt_plan_ranges.restype = C.c_int
@@ -152,6 +154,41 @@ def bind(*, out, queries, locations, keys, values, scale, fragment_lengths=None,
 
 def workspace_bytes(bp: BoundProblem) -> int:
     return int(load().hogatt_workspace_bytes(C.byref(bp.struct)))
+
+
+def describe(bp: BoundProblem, num_sms: int) -> dict:
+    """``hogatt_plan_describe`` for a bound problem, taking every row of every fragment as visible."""
+    F = bp.struct.F
+    vis = (C.c_int32 * F)(*[bp.struct.fragment_rows[f] for f in range(F)])
+    plan = (C.c_int32 * 8)()
+    rc = int(load().hogatt_plan_describe(C.byref(bp.struct), vis, num_sms, plan))
+    if rc != 0:
+        raise ValueError(status_string(rc))
+    keys = ("tile_tokens", "rows_per_block", "row_blocks", "tiles_per_unit", "units", "ctas", "parts_per_unit", "kernel")
+    return dict(zip(keys, list(plan)))
+
+
+def launch_shape(bp: BoundProblem) -> dict:
+    """``hogatt_launch_shape``: what one launch of this problem enqueues on the current device."""
+    shape = (C.c_int32 * 4)()
+    rc = int(load().hogatt_launch_shape(C.byref(bp.struct), shape))
+    if rc != 0:
+        raise ValueError(status_string(rc))
+    return dict(zip(("kernel", "ctas", "cluster", "kernels_per_call"), list(shape)))
+
+
+def attach_workspace(bp: BoundProblem, device, stream: int = 0):
+    """Allocate (torch), align and bind the scratch a problem needs; returns the tensor that owns the
+    memory (also kept alive by ``bp``)."""
+    import torch
+    need = workspace_bytes(bp)
+    if need == 0:
+        raise ValueError("libhogatt_b200 refused the problem")
+    ws = torch.empty(need + 256, dtype=torch.uint8, device=device)
+    ptr = ws.data_ptr() + (-ws.data_ptr()) % 256
+    bp.struct.workspace, bp.struct.workspace_bytes = ptr, need
+    bp._keep.append(ws)
+    return ws
 
 
 STATIC_SCRATCH_BYTES = 8 << 20

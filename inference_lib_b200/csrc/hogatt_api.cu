@@ -101,6 +101,9 @@ struct Resolved {
     int tile_tokens;
     int row_blocks;
     int units;
+    int cluster_mode;    // -1 never (HOGATT_KERNEL_MMA), 0 let choose_cluster decide (AUTO), 1 required (HOGATT_KERNEL_MMA_CLUSTER)
+    int cluster;         // CTAs per cluster of the self-merging variant, 0 = persistent grid + merge kernel
+    bool cluster_forced;
 };
 
 bool mma_eligible(const hogatt_problem* p) {
@@ -126,12 +129,16 @@ int resolve(const hogatt_problem* p, Resolved* r) {
     const int64_t rows_total = (int64_t)p->W * (p->Hq / p->Hkv) * p->S;
     if (rows_total > (1 << 24) || (int64_t)p->F * p->W * p->S > (1 << 26)) return HOGATT_ERR_TOO_LARGE;
     int kernel = p->kernel;
+    r->cluster_mode = kernel == HOGATT_KERNEL_MMA ? -1 : (kernel == HOGATT_KERNEL_MMA_CLUSTER ? 1 : 0);
+    r->cluster = 0;
+    r->cluster_forced = kernel == HOGATT_KERNEL_MMA_CLUSTER;
+    if (kernel == HOGATT_KERNEL_MMA_CLUSTER) kernel = HOGATT_KERNEL_MMA;
     if (kernel == HOGATT_KERNEL_AUTO) kernel = mma_eligible(p) ? HOGATT_KERNEL_MMA : HOGATT_KERNEL_FMA;
     if (kernel == HOGATT_KERNEL_MMA) {
         if (!mma_eligible(p)) return HOGATT_ERR_BAD_KERNEL_CHOICE;
         r->mt = rows_total <= 16 ? 1 : (rows_total <= 32 ? 2 : 4);
         r->rows_per_block = 16 * r->mt;
-        r->tile_tokens = p->E == 128 ? 64 : 128;
+        r->tile_tokens = p->E == 128 ? 128 : 256;
     } else if (kernel == HOGATT_KERNEL_FMA) {
         if (!fma_eligible(p)) return HOGATT_ERR_UNSUPPORTED_HEAD_DIM;
         r->mt = 1;
@@ -165,6 +172,20 @@ WorkspaceLayout carve(const hogatt_problem* p, const Resolved& r, int grid) {
     return w;
 }
 
+// Largest cluster the self-merging variant could use if every cluster size up to 16 were available:
+// host-only bound, for hogatt_plan_describe.
+int cluster_upper_bound(const Resolved& r, int sms) {
+    if (r.kernel != HOGATT_KERNEL_MMA || r.cluster_mode < 0) return 0;
+    const int cs = std::min(16, sms / std::max(r.units, 1));
+    return cs >= 2 ? cs : 0;
+}
+
+int64_t tiles_upper_bound(const hogatt_problem* p, const Resolved& r) {
+    int64_t th = 0;
+    for (int f = 0; f < p->F; ++f) th += ceil_div(p->fragment_rows[f] < 0 ? 0 : p->fragment_rows[f], r.tile_tokens);
+    return th;
+}
+
 int grid_size(const hogatt_problem* p, int sms) {
     int grid = sms;
     if (p->max_ctas > 0 && p->max_ctas < grid) grid = p->max_ctas;
@@ -173,30 +194,154 @@ int grid_size(const hogatt_problem* p, int sms) {
 
 // ---- launch helpers, one per kernel family ------------------------------------------------------
 
+// Upper limit on CTAs per cluster: 16 (the hardware's), or HOGATT_MAX_CLUSTER from the environment
+// (2..16, read when the library is first used; for experiments with the cluster shape).
+int max_cluster_size() {
+    static const int cap = [] {
+        const char* v = getenv("HOGATT_MAX_CLUSTER");
+        const int n = v ? atoi(v) : 16;
+        return n < 2 ? 2 : (n > 16 ? 16 : n);
+    }();
+    return cap;
+}
+
+// How many clusters of `cs` CTAs of the cluster variant the device holds at once (0 on failure), asked
+// once per (kernel instantiation, device, size).  It depends on how the SMs are grouped on the part: a
+// B200 with one ~200 KB CTA per SM holds 74 clusters of 2, 33 of 4, 15 of 8 or 9, 11 of 10, 7 of 11..16.
 template <class T, int HD, int MT>
-int launch_mma(const KernelArgs& args, int F, int dev, int smem_optin, int grid, bool evict_first, cudaStream_t stream) {
+std::atomic<size_t>* cluster_smem_granted() {
     static std::atomic<size_t> granted[kMaxDevices];
+    return granted;
+}
+
+template <class T, int HD, int MT>
+int mma_resident_clusters(int dev, size_t smem, int cs) {
+    std::atomic<size_t>* granted = cluster_smem_granted<T, HD, MT>();
+    static std::atomic<int> wide_ok[kMaxDevices];                      // clusters of more than 8 CTAs are opt-in
+    static std::atomic<int> resident[kMaxDevices][17];                 // +1; 0 = not asked yet
+    using C = MmaCfg<HD, MT>;
+    auto kernel = mma_attention_kernel<T, HD, MT, true>;
+    int have = resident[dev][cs].load(std::memory_order_acquire);
+    if (have) return have - 1;
+    if (ensure_smem_limit(kernel, dev, smem, granted) != HOGATT_OK) return 0;
+    if (!wide_ok[dev].load(std::memory_order_acquire)) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) return 0;
+        wide_ok[dev].store(1, std::memory_order_release);
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(cs);
+    cfg.blockDim = dim3(C::THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)cs;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        n = 0;
+    }
+    resident[dev][cs].store(n + 1, std::memory_order_release);
+    return n;
+}
+
+// The largest cluster size (2..16) at which one cluster per unit is resident all at once; 0 if none.
+template <class T, int HD, int MT>
+int mma_best_cluster(int dev, int F, int smem_optin, int units, int sms) {
+    const size_t smem = mma_smem_bytes<HD, MT>(F);
+    if (smem > (size_t)smem_optin) return 0;
+    for (int cs = std::min(max_cluster_size(), sms / std::max(units, 1)); cs >= 2; --cs)
+        if (mma_resident_clusters<T, HD, MT>(dev, smem, cs) >= units) return cs;
+    return 0;
+}
+
+template <class T>
+int mma_best_cluster_dims(int HD, int MT, int dev, int F, int smem_optin, int units, int sms) {
+    if (HD == 128) {
+        if (MT == 1) return mma_best_cluster<T, 128, 1>(dev, F, smem_optin, units, sms);
+        if (MT == 2) return mma_best_cluster<T, 128, 2>(dev, F, smem_optin, units, sms);
+        return mma_best_cluster<T, 128, 4>(dev, F, smem_optin, units, sms);
+    }
+    if (MT == 1) return mma_best_cluster<T, 64, 1>(dev, F, smem_optin, units, sms);
+    if (MT == 2) return mma_best_cluster<T, 64, 2>(dev, F, smem_optin, units, sms);
+    return mma_best_cluster<T, 64, 4>(dev, F, smem_optin, units, sms);
+}
+
+// CTAs per cluster if this problem runs as the self-merging cluster variant on the current device, else 0
+// (persistent grid + merge kernel).  The cluster variant saves the partials' trip through the workspace
+// and the second launch, but it only uses units * cluster SMs and one SM pulls about 66 GB/s: it wins
+// where the fixed costs dominate.  Fitted to measurements on B200 at 8 kv heads (us per call, B bytes
+// streamed, n CTAs; beyond 64 CTAs -- clusters of 10 -- the cluster shape did not get faster):
+//   persistent grid ~ 11.4 + B / 6.07 TB/s        cluster ~ 8.5 + B / (min(n, 64) * 66 GB/s)
+// i.e. the cluster shape below about 40 MB per call (8K keys at 8 kv heads of 128), the persistent grid above.
+constexpr double kPersistFixedUs = 11.4, kClusterFixedUs = 8.5, kChipBytesPerUs = 6.07e6, kSmBytesPerUs = 66e3;
+constexpr int kClusterUsefulCtas = 64;
+int choose_cluster(const hogatt_problem* p, const Resolved& r, int dev, int sms, int smem_optin, int64_t tiles_per_unit) {
+    if (r.kernel != HOGATT_KERNEL_MMA || r.cluster_mode < 0 || 2 * r.units > sms) return 0;
+    int cs = 0;
+    if (p->dtype == HOGATT_F16) cs = mma_best_cluster_dims<__half>(p->E, r.mt, dev, p->F, smem_optin, r.units, sms);
+    if (p->dtype == HOGATT_BF16) cs = mma_best_cluster_dims<__nv_bfloat16>(p->E, r.mt, dev, p->F, smem_optin, r.units, sms);
+    if (cs == 0 || r.cluster_mode > 0) return cs;
+    if (p->max_ctas > 0) return 0;                       // the caller is testing grid sizes of the persistent variant
+    cs = std::min(cs, std::max(2, kClusterUsefulCtas / r.units));
+    const double bytes = (double)tiles_per_unit * r.units * MmaCfg<128, 1>::STAGE_BYTES;
+    const double persistent = kPersistFixedUs + bytes / kChipBytesPerUs;
+    const double cluster = kClusterFixedUs + bytes / (kSmBytesPerUs * std::min(r.units * cs, kClusterUsefulCtas));
+    return cluster < persistent ? cs : 0;
+}
+
+// cluster == 0: persistent grid of `grid` CTAs (merge_kernel must follow).
+// cluster >= 2: units * cluster CTAs in clusters of `cluster`; the kernel merges by itself.
+template <class T, int HD, int MT>
+int launch_mma(const KernelArgs& args, int F, int dev, int smem_optin, int grid, int cluster, bool evict_first,
+               cudaStream_t stream) {
     using C = MmaCfg<HD, MT>;
     const size_t smem = mma_smem_bytes<HD, MT>(F);
     if (smem > (size_t)smem_optin) return HOGATT_ERR_TOO_MANY_FRAGMENTS;
-    int rc = ensure_smem_limit(mma_attention_kernel<T, HD, MT>, dev, smem, granted);
+    if (cluster == 0) {
+        static std::atomic<size_t> granted[kMaxDevices];
+        int rc = ensure_smem_limit(mma_attention_kernel<T, HD, MT, false>, dev, smem, granted);
+        if (rc != HOGATT_OK) return rc;
+        HOGATT_CUDA_OK(launch_kernel(mma_attention_kernel<T, HD, MT, false>, dim3(grid), dim3(C::THREADS), smem, stream,
+                                     args, evict_first ? 1 : 0));
+        return HOGATT_OK;
+    }
+    // the wide-cluster opt-in was set when choose_cluster() asked for the residency; the shared-memory limit
+    // too, but for the fragment count of that call
+    int rc = ensure_smem_limit(mma_attention_kernel<T, HD, MT, true>, dev, smem, cluster_smem_granted<T, HD, MT>());
     if (rc != HOGATT_OK) return rc;
-    HOGATT_CUDA_OK(launch_kernel(mma_attention_kernel<T, HD, MT>, dim3(grid), dim3(C::THREADS), smem, stream, args,
-                                 evict_first ? 1 : 0));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(C::THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)cluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    HOGATT_CUDA_OK(cudaLaunchKernelEx(&cfg, mma_attention_kernel<T, HD, MT, true>, args, (int)(evict_first ? 1 : 0)));
     return HOGATT_OK;
 }
 
 template <class T>
-int launch_mma_dims(const KernelArgs& args, int F, int HD, int MT, int dev, int smem_optin, int grid, bool ef,
+int launch_mma_dims(const KernelArgs& args, int F, int HD, int MT, int dev, int smem_optin, int grid, int cluster, bool ef,
                     cudaStream_t stream) {
     if (HD == 128) {
-        if (MT == 1) return launch_mma<T, 128, 1>(args, F, dev, smem_optin, grid, ef, stream);
-        if (MT == 2) return launch_mma<T, 128, 2>(args, F, dev, smem_optin, grid, ef, stream);
-        return launch_mma<T, 128, 4>(args, F, dev, smem_optin, grid, ef, stream);
+        if (MT == 1) return launch_mma<T, 128, 1>(args, F, dev, smem_optin, grid, cluster, ef, stream);
+        if (MT == 2) return launch_mma<T, 128, 2>(args, F, dev, smem_optin, grid, cluster, ef, stream);
+        return launch_mma<T, 128, 4>(args, F, dev, smem_optin, grid, cluster, ef, stream);
     }
-    if (MT == 1) return launch_mma<T, 64, 1>(args, F, dev, smem_optin, grid, ef, stream);
-    if (MT == 2) return launch_mma<T, 64, 2>(args, F, dev, smem_optin, grid, ef, stream);
-    return launch_mma<T, 64, 4>(args, F, dev, smem_optin, grid, ef, stream);
+    if (MT == 1) return launch_mma<T, 64, 1>(args, F, dev, smem_optin, grid, cluster, ef, stream);
+    if (MT == 2) return launch_mma<T, 64, 2>(args, F, dev, smem_optin, grid, cluster, ef, stream);
+    return launch_mma<T, 64, 4>(args, F, dev, smem_optin, grid, cluster, ef, stream);
 }
 
 template <class T, int EV>
@@ -224,10 +369,14 @@ int launch_fma_dims(const KernelArgs& args, int dev, int smem_optin, int grid, c
 template <class T>
 int launch_all(const KernelArgs& args, const Resolved& r, int dev, int smem_optin, int grid, cudaStream_t stream) {
     int rc;
-    if (r.kernel == HOGATT_KERNEL_MMA)
-        rc = launch_mma_dims<T>(args, args.F, args.E, r.mt, dev, smem_optin, grid, /*evict_first=*/r.row_blocks == 1, stream);
-    else
+    if (r.kernel == HOGATT_KERNEL_MMA) {
+        const bool ef = r.row_blocks == 1;       // every K/V byte is read once: do not let it displace L2 contents
+        if (r.cluster > 1)      // the cluster kernel merges by itself
+            return launch_mma_dims<T>(args, args.F, args.E, r.mt, dev, smem_optin, r.units * r.cluster, r.cluster, ef, stream);
+        rc = launch_mma_dims<T>(args, args.F, args.E, r.mt, dev, smem_optin, grid, 0, ef, stream);
+    } else {
         rc = launch_fma_dims<T>(args, dev, smem_optin, grid, stream);
+    }
     if (rc != HOGATT_OK) return rc;
 #ifdef HOGATT_EXPERIMENT
     if (getenv("HOGATT_SKIP_MERGE")) return HOGATT_OK;
@@ -280,6 +429,8 @@ int attention_launch(const hogatt_problem* p, bool fused, cudaStream_t stream, c
     const int grid = grid_size(p, sms);
     const WorkspaceLayout w = carve(p, r, grid);
     if (p->workspace_bytes < w.total) return HOGATT_ERR_WORKSPACE_TOO_SMALL;
+    r.cluster = choose_cluster(p, r, dev, sms, smem_optin, tiles_upper_bound(p, r));
+    if (r.cluster_forced && r.cluster == 0) return HOGATT_ERR_BAD_KERNEL_CHOICE;
 
     KernelArgs args;
     memset(&args, 0, sizeof(args));
@@ -628,14 +779,34 @@ int hogatt_plan_describe(const hogatt_problem* p, const int32_t* visible_rows, i
     for (int f = 0; f < p->F; ++f) th += ceil_div(visible_rows[f] < 0 ? 0 : visible_rows[f], r.tile_tokens);
     if (th > (1 << 30)) return HOGATT_ERR_TOO_LARGE;
     const int grid = grid_size(p, num_sms);
+    const int cluster = r.cluster_forced ? cluster_upper_bound(r, num_sms) : 0;
+    if (r.cluster_forced && cluster == 0) return HOGATT_ERR_BAD_KERNEL_CHOICE;
     plan[0] = r.tile_tokens;
     plan[1] = r.rows_per_block;
     plan[2] = r.row_blocks;
     plan[3] = (int)th;
     plan[4] = r.units;
-    plan[5] = effective_ctas((int64_t)r.units * th, grid);
-    plan[6] = max_parts_per_unit(r.units, grid);
-    plan[7] = r.kernel;
+    plan[5] = cluster ? r.units * cluster : effective_ctas((int64_t)r.units * th, grid);
+    plan[6] = cluster ? cluster : max_parts_per_unit(r.units, grid);
+    plan[7] = cluster ? HOGATT_KERNEL_MMA_CLUSTER : r.kernel;
+    return HOGATT_OK;
+}
+
+int hogatt_launch_shape(const hogatt_problem* p, int32_t shape[4]) {
+    Resolved r;
+    int rc = resolve(p, &r);
+    if (rc != HOGATT_OK) return rc;
+    if (!shape || !p->fragment_rows) return HOGATT_ERR_NULL_POINTER;
+    int dev, sms, smem_optin;
+    rc = current_device_info(&dev, &sms, &smem_optin);
+    if (rc != HOGATT_OK) return rc;
+    const int grid = grid_size(p, sms);
+    const int cluster = choose_cluster(p, r, dev, sms, smem_optin, tiles_upper_bound(p, r));
+    if (r.cluster_forced && cluster == 0) return HOGATT_ERR_BAD_KERNEL_CHOICE;
+    shape[0] = cluster ? HOGATT_KERNEL_MMA_CLUSTER : r.kernel;
+    shape[1] = cluster ? r.units * cluster : grid;
+    shape[2] = cluster;
+    shape[3] = cluster ? 1 : 2;
     return HOGATT_OK;
 }
 

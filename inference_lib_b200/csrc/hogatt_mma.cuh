@@ -56,6 +56,14 @@ struct MmaCfg {
     static constexpr int SLOT_FLOATS = NT_O * 4 * 32;    // one warp's accumulators
     static constexpr int QPITCH = ROWB + 16;             // bytes per staged query row (padding: conflict-free ldmatrix)
     static constexpr int QBYTES = RPB * QPITCH;
+    // cluster variant: what a CTA leaves in its own shared memory for the cluster-wide merge
+    static constexpr int OPITCH = HD + 8;                // floats per partial row (padding: conflict-free float2 stores)
+    static constexpr int CL_PART_FLOATS = 16 * OPITCH;   // one warp's 16 rows
+    static constexpr int CL_STAT = NCW * CL_PART_FLOATS; // float offset of the row maxima [NCW][16], sums follow
+    static constexpr int CL_ACC = CL_STAT + 2 * NCW * 16;        // merge scratch [tasks <= RPB][HD]
+    static constexpr int CL_DEN = CL_ACC + RPB * HD;             // [tasks]
+    static constexpr int CL_FLOATS = CL_DEN + RPB;
+    static_assert(CL_FLOATS * 4 <= NSTAGE * STAGE_BYTES, "cluster merge scratch must fit in the stage ring");
     static_assert(NT_S >= 2 && NT_S % 2 == 0, "a warp's slice must hold whole k16 steps");
     static_assert(NCW * SLOT_FLOATS * 4 <= STAGE_BYTES, "fold scratch must fit in one stage");
     static_assert(NT_O % NSLICE == 0, "output columns must split evenly over the slices");
@@ -69,7 +77,33 @@ __host__ __device__ inline size_t mma_smem_bytes(int F) {
            ((size_t)2 * F + 1) * 4;
 }
 
-template <class T, int HD, int MT>
+// Destinations of a finished output row: this rank's `out`, or (fused all-gather) the full-size output of
+// every rank at this rank's head offset.
+template <class T>
+struct OutputTargets {
+    T* const* bases;
+    T* local;
+    int nbases, hq_all, hq_off;
+    __device__ __forceinline__ explicit OutputTargets(const KernelArgs& a) : local(static_cast<T*>(a.out)) {
+        nbases = a.world > 0 ? a.world : 1;
+        hq_all = a.world > 0 ? a.world * a.Hq : a.Hq;
+        hq_off = a.world > 0 ? a.rank * a.Hq : 0;
+        bases = a.world > 0 ? reinterpret_cast<T* const*>(a.peer_out) : nullptr;
+    }
+    __device__ __forceinline__ T* base(int b) const { return bases ? bases[b] : local; }
+    // element offset of row (w, local head hq, s)
+    __device__ __forceinline__ size_t row_offset(int w, int hq, int s, int S, int Ev) const {
+        return ((size_t)(w * hq_all + hq_off + hq) * S + s) * Ev;
+    }
+};
+
+// CL = false: persistent grid over balanced tile ranges, partials to the workspace, merge_kernel follows.
+// CL = true : launched in thread-block clusters, one cluster per (kv head, row block) unit; CTA `rank`
+//             of the cluster takes tiles [rank*TH/CS, (rank+1)*TH/CS) of the unit; every warp leaves its
+//             private (O, max, sum) in its CTA's shared memory, and after a cluster barrier CTA `rank`
+//             merges rows rank, rank+CS, ... of the block over ALL warps of ALL CTAs through distributed
+//             shared memory and stores the final rows: no workspace traffic, no second kernel.
+template <class T, int HD, int MT, bool CL>
 __global__ void __launch_bounds__(MmaCfg<HD, MT>::THREADS, 1)
 mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_first) {
     using C = MmaCfg<HD, MT>;
@@ -116,8 +150,9 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
     const int TH = pre[a.F];
     const int units = a.row_blocks * a.Hkv;
     const int64_t N = (int64_t)units * TH;
-    const int ctas = effective_ctas(N, gridDim.x);
-    if (blockIdx.x == 0 && tid == 0) {
+    const int ctas = CL ? (int)gridDim.x : effective_ctas(N, gridDim.x);
+    const int CS = CL ? (int)cluster_nctarank() : 1, crank = CL ? (int)cluster_ctarank() : 0;
+    if (!CL && blockIdx.x == 0 && tid == 0) {
         a.header[0] = TH;
         a.header[1] = ctas;
     }
@@ -132,7 +167,15 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
     }
     if (warp <= 1) HOGATT_TL(warp, 3);
 
-    const int64_t t0 = cta_first_tile(blockIdx.x, N, ctas), t1 = cta_first_tile(blockIdx.x + 1, N, ctas);
+    int64_t t0, t1;
+    if constexpr (CL) {
+        const int64_t ubase = (int64_t)(blockIdx.x / CS) * TH;
+        t0 = ubase + (int64_t)crank * TH / CS;
+        t1 = ubase + (int64_t)(crank + 1) * TH / CS;
+    } else {
+        t0 = cta_first_tile(blockIdx.x, N, ctas);
+        t1 = cta_first_tile(blockIdx.x + 1, N, ctas);
+    }
 
     // =====================================================================================
     // Producer warp
@@ -140,7 +183,7 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
     if (warp == 0) {
         uint64_t policy = 0;
         if (use_evict_first) policy = l2_policy_evict_first();
-        int64_t u = t0 / TH;
+        int64_t u = CL ? (int64_t)(blockIdx.x / CS) : t0 / TH;
         int j = (int)(t0 - u * TH), fscan = 0, it = 0;
         bool ok = true;
         for (int64_t t = t0; t < t1 && ok; ++t, ++it) {
@@ -186,6 +229,10 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
                                   STATUS_DRAIN_TIMEOUT);
         }
         HOGATT_SPAN_MAX(1);
+        if constexpr (CL) {
+            cluster_sync_all();      // partials of every CTA are in place
+            cluster_sync_all();      // nobody reads this CTA's shared memory any more
+        }
         return;
     }
 
@@ -214,7 +261,7 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
         return __all_sync(0xffffffffu, ok);
     };
 
-    int64_t u = t0 / TH;
+    int64_t u = CL ? (int64_t)(blockIdx.x / CS) : t0 / TH;
     int j = (int)(t0 - u * TH), fscan = 0, it = 0, cur_u = -1, cur_f = -1, hkv = 0, rb = 0;
     for (int64_t t = t0; t < t1; ++t, ++it) {
         if ((int)u != cur_u) {
@@ -419,7 +466,7 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
         // ---- end of this CTA's share of the unit: fold the warps together, leave a partial ----
         const bool last = (j == TH - 1) || (t == t1 - 1);
         bool wrote_scratch = false;
-        if (last) {
+        if (!CL && last) {
             l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
             l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
             l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
@@ -497,6 +544,131 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
             j = 0;
             ++u;
         }
+    }
+    if constexpr (CL) {
+        constexpr int CTHREADS = C::NCW * 32;
+        if (want_rq && it == 0)          // a CTA without tiles still writes its share of the rotated queries
+            write_rotated_queries<T>(a.q, a.rq, a.cos, a.sin, a.F, a.W, a.Hq, a.S, HD, a.R,
+                                     blockIdx.x * CTHREADS + tid - 32, gridDim.x * CTHREADS);
+        // ---- leave this warp's private result in shared memory ----
+        l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
+        l_a += __shfl_xor_sync(0xffffffffu, l_a, 2);
+        l_b += __shfl_xor_sync(0xffffffffu, l_b, 1);
+        l_b += __shfl_xor_sync(0xffffffffu, l_b, 2);
+        if (it == 0) {                   // the accumulators were never initialised
+            m_a = m_b = -INFINITY;
+            l_a = l_b = 0.f;
+#pragma unroll
+            for (int n = 0; n < C::NT_O; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+        }
+        float* const scr = reinterpret_cast<float*>(stages);
+        named_barrier_sync(1, CTHREADS);                  // every consumer warp is done with the K/V stages
+        {
+            float* part = scr + (size_t)cw * C::CL_PART_FLOATS;
+#pragma unroll
+            for (int n = 0; n < C::NT_O; ++n) {
+                *reinterpret_cast<float2*>(part + quad * C::OPITCH + n * 8 + qlane * 2) = make_float2(o[n][0], o[n][1]);
+                *reinterpret_cast<float2*>(part + (quad + 8) * C::OPITCH + n * 8 + qlane * 2) = make_float2(o[n][2], o[n][3]);
+            }
+            if (qlane == 0) {
+                scr[C::CL_STAT + cw * 16 + quad] = m_a;
+                scr[C::CL_STAT + cw * 16 + quad + 8] = m_b;
+                scr[C::CL_STAT + C::NCW * 16 + cw * 16 + quad] = l_a;
+                scr[C::CL_STAT + C::NCW * 16 + cw * 16 + quad + 8] = l_b;
+            }
+        }
+        cluster_sync_all();
+        if (warp == 1) HOGATT_TL(1, 901);
+
+        // ---- merge rows crank, crank + CS, ... of the block over every warp of every CTA ----
+        const int P = CS * C::NSLICE;                     // partials per row (<= 64)
+        const int RC = (C::RPB - crank + CS - 1) / CS;    // rows this CTA finishes (CS <= 16 <= RPB: at least one)
+        const int SPLIT = max(1, C::NCW / ((C::RPB + CS - 1) / CS));   // warps sharing one row, each takes partials p % SPLIT == sub
+        const int ntask = RC * SPLIT;
+        const uint32_t scr_addr = smem_u32(scr);
+        for (int task = cw; task < ntask; task += C::NCW) {
+            const int ri = task / SPLIT, sub = task % SPLIT;
+            const int r = crank + ri * CS;
+            const int mt_r = r >> 4, rr = r & 15;
+            float mp[2], lp[2];
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                const int p = lane + 32 * k;
+                mp[k] = -INFINITY;
+                lp[k] = 0.f;
+                if (p < P) {
+                    const int wp = (p % C::NSLICE) * MT + mt_r;
+                    const uint32_t ad = map_to_cta(scr_addr + (C::CL_STAT + wp * 16 + rr) * 4, p / C::NSLICE);
+                    mp[k] = ld_cluster_f(ad);
+                    lp[k] = ld_cluster_f(ad + C::NCW * 16 * 4);
+                }
+            }
+            float M = fmaxf(mp[0], mp[1]);
+#pragma unroll
+            for (int sh = 16; sh > 0; sh >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, sh));
+            const float mu = (M == -INFINITY) ? 0.f : M;
+            const float w0 = exp2f(mp[0] - mu), w1 = exp2f(mp[1] - mu);
+            float den = lp[0] * w0 + lp[1] * w1;
+#pragma unroll
+            for (int sh = 16; sh > 0; sh >>= 1) den += __shfl_xor_sync(0xffffffffu, den, sh);
+            const bool act = lane * 4 < HD;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            constexpr int UNR = 8;
+            for (int p0 = sub; p0 < P; p0 += SPLIT * UNR) {
+                float4 x[UNR];
+#pragma unroll
+                for (int i = 0; i < UNR; ++i) {
+                    const int p = p0 + i * SPLIT;
+                    x[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (p < P && act) {
+                        const int wp = (p % C::NSLICE) * MT + mt_r;
+                        x[i] = ld_cluster_f4(map_to_cta(
+                            scr_addr + (wp * C::CL_PART_FLOATS + rr * C::OPITCH + lane * 4) * 4, p / C::NSLICE));
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < UNR; ++i) {
+                    const int p = p0 + i * SPLIT;
+                    const float wgt = __shfl_sync(0xffffffffu, (p & 32) ? w1 : w0, p & 31);
+                    acc.x = fmaf(x[i].x, wgt, acc.x);
+                    acc.y = fmaf(x[i].y, wgt, acc.y);
+                    acc.z = fmaf(x[i].z, wgt, acc.z);
+                    acc.w = fmaf(x[i].w, wgt, acc.w);
+                }
+            }
+            if (act) *reinterpret_cast<float4*>(scr + C::CL_ACC + task * HD + lane * 4) = acc;
+            if (lane == 0) scr[C::CL_DEN + task] = den;
+        }
+        named_barrier_sync(1, CTHREADS);
+        {
+            const int unit = (int)(blockIdx.x / CS);
+            const int rb_u = unit / a.Hkv, hkv_u = unit % a.Hkv;
+            const OutputTargets<T> dst(a);
+            for (int item = tid - 32; item < RC * (HD / 4); item += CTHREADS) {
+                const int ri = item / (HD / 4), c4 = item % (HD / 4);
+                const int gr = rb_u * C::RPB + crank + ri * CS;
+                if (gr >= a.rows_total) continue;
+                float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int sub = 0; sub < SPLIT; ++sub) {
+                    const float4 y = *reinterpret_cast<const float4*>(scr + C::CL_ACC + (ri * SPLIT + sub) * HD + c4 * 4);
+                    sum.x += y.x;
+                    sum.y += y.y;
+                    sum.z += y.z;
+                    sum.w += y.w;
+                }
+                const float den = scr[C::CL_DEN + ri * SPLIT];
+                const float inv = den > 0.f ? 1.f / den : 0.f;
+                if (!(den > 0.f)) sum = make_float4(0.f, 0.f, 0.f, 0.f);
+                const RowId id = decode_row(gr, a.G, a.S);
+                const size_t offset = dst.row_offset(id.w, hkv_u * a.G + id.g, id.s, a.S, HD) + c4 * 4;
+                uint2 packed;
+                packed.x = pack2<T>(sum.x * inv, sum.y * inv);
+                packed.y = pack2<T>(sum.z * inv, sum.w * inv);
+                for (int b = 0; b < dst.nbases; ++b) *reinterpret_cast<uint2*>(dst.base(b) + offset) = packed;
+            }
+        }
+        if (warp == 1) HOGATT_TL(1, 902);
+        cluster_sync_all();              // no CTA leaves while another may still read its shared memory
     }
 #ifdef HOGATT_TIMELINE
     if (warp == 1 && lane == 0) {

@@ -51,9 +51,17 @@ def test_plan_for_the_headline_shapes(lib):
     rc, plan = _describe(lib, [8192, 2048, 2048, 2048, 2048], F=5, W=4, Hq=32, Hkv=8, E=128, Ev=128, S=1, dtype=_cabi.BF16)
     assert rc == 0
     tile, rows, row_blocks, th, units, ctas, parts, kernel = plan
-    assert (tile, rows, row_blocks, th, units, ctas, kernel) == (64, 16, 1, 256, 8, 148, _cabi.KERNEL_MMA)
+    assert (tile, rows, row_blocks, th, units, ctas, parts, kernel) == (128, 16, 1, 128, 8, 148, 148 // 8 + 2, _cabi.KERNEL_MMA)
+    # the cluster launch shape only on request: one cluster of up to 16 CTAs per kv head, merged inside the kernel
+    rc, plan = _describe(lib, [8192, 2048, 2048, 2048, 2048], F=5, W=4, Hq=32, Hkv=8, E=128, Ev=128, S=1, dtype=_cabi.BF16,
+                         kernel=_cabi.KERNEL_MMA_CLUSTER)
+    assert rc == 0 and plan[5] == 128 and plan[6] == 16 and plan[7] == _cabi.KERNEL_MMA_CLUSTER
+    # long context: persistent grid over all SMs
     rc, plan = _describe(lib, [131072, 4096, 4096], F=3, W=2, Hq=32, Hkv=8, E=128, Ev=128, S=1, dtype=_cabi.BF16)
-    assert rc == 0 and plan[3] == 2176 and plan[5] == 148          # 2176 tiles per head >= 64 chunks per head
+    assert rc == 0 and plan[3] == 1088 and plan[5] == 148 and plan[7] == _cabi.KERNEL_MMA   # 1088 tiles per head >= 64 chunks per head
+    # the cluster shape needs at least two CTAs per unit
+    rc, plan = _describe(lib, [1024], F=1, W=8, Hq=64, Hkv=8, E=128, Ev=128, S=16, dtype=_cabi.BF16, kernel=_cabi.KERNEL_MMA_CLUSTER)
+    assert rc == -9
     rc, plan = _describe(lib, [256, 64, 64], F=3, W=2, Hq=8, Hkv=2, E=64, Ev=64, S=1, dtype=_cabi.F32)
     assert rc == 0 and plan[7] == _cabi.KERNEL_FMA and plan[0] == 32
     rc, plan = _describe(lib, [16384] + [1024] * 8, F=9, W=8, Hq=64, Hkv=8, E=128, Ev=128, S=16, dtype=_cabi.BF16)

@@ -31,11 +31,8 @@ def _rank_main(rank, world, port, name, q):
         out_local = torch.empty((d.W, d.Hq, d.S, d.Ev), dtype=d.dtype, device=dev)
         bp = _cabi.bind(out=out_local, queries=d.queries, locations=d.locations, keys=d.keys, values=d.values,
                         scale=d.scale, fragment_lengths=d.fragment_lengths, cos=d.cos, sin=d.sin, status=status)
-        need = _cabi.workspace_bytes(bp)
-        ws = torch.empty(need + 256, dtype=torch.uint8, device=dev)
-        bp.struct.workspace = ws.data_ptr() + (-ws.data_ptr()) % 256
-        bp.struct.workspace_bytes = need
         stream = torch.cuda.current_stream(dev).cuda_stream
+        _cabi.attach_workspace(bp, dev, stream)
         # (1) NCCL baseline
         assert _cabi.launch(bp, stream) == 0
         nccl_full = sharded.gather_heads(out_local, world)

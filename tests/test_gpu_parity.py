@@ -13,10 +13,15 @@ pytestmark = pytest.mark.gpu
 CFG5_SLICE = (slice(None), slice(None, None, 8), slice(None, None, 4), slice(None))
 
 
-def _kernels_for(p):
+def _kernels_for(p, cluster=True):
     ks = []
     if p.dtype != torch.float32 and p.E == p.Ev and p.E in (64, 128):
         ks.append(_cabi.KERNEL_MMA)
+        rows = p.W * (p.Hq // p.Hkv) * p.S
+        rows_per_block = 16 if rows <= 16 else (32 if rows <= 32 else 64)
+        units = -(-rows // rows_per_block) * p.Hkv
+        if cluster and 2 * units <= torch.cuda.get_device_properties(0).multi_processor_count:
+            ks.append(_cabi.KERNEL_MMA_CLUSTER)      # same kernel, launched in clusters that merge by themselves
     if p.Ev in (32, 64, 128, 256):
         ks.append(_cabi.KERNEL_FMA)
     return ks
@@ -28,6 +33,67 @@ def test_baseline_shapes_match_reference(golden, name):
     r = run_cabi(p)
     assert r.rc == 0 and r.status == 0
     check_against(r.out, golden[f"{name}/out"], p.dtype, what=name)
+
+
+@pytest.mark.parametrize("name", ["cfg2", "cfg3", "target", "cfg4"])
+@pytest.mark.parametrize("kernel", [_cabi.KERNEL_MMA, _cabi.KERNEL_MMA_CLUSTER])
+def test_both_launch_shapes_of_the_tensor_core_kernel(golden, name, kernel):
+    p = wl.baseline_problem(name)
+    r = run_cabi(p, kernel=kernel, want_rq=True)
+    assert r.rc == 0 and r.status == 0
+    check_against(r.out, golden[f"{name}/out"], p.dtype, what=f"{name} kernel {kernel}")
+    if f"{name}/rq" in golden.files:
+        assert np.array_equal(r.rq.float().cpu().numpy(), golden[f"{name}/rq"])
+
+
+def test_cluster_shape_is_refused_when_units_exceed_half_the_sms():
+    p = wl.baseline_problem("cfg5", seed=0)          # 128 units
+    r = run_cabi(p, kernel=_cabi.KERNEL_MMA_CLUSTER)
+    assert r.rc == -9
+
+
+def test_one_workspace_serves_many_launches_and_shapes(golden):
+    """The workspace carries nothing from one launch to the next: any contents, any sequence of shapes."""
+    names = ["cfg2", "target", "ragged_bf16", "cfg3", "cfg2", "gqa5_bf16", "target"]
+    dev = torch.device("cuda:0")
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    ws = torch.full((64 << 20,), 0x5A, dtype=torch.uint8, device=dev)
+    ptr = ws.data_ptr() + (-ws.data_ptr()) % 256
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    for name in names:
+        p = wl.baseline_problem(name) if name in wl.BASELINE_CONFIGS else wl.edge_problem(name)
+        d = p.to(dev)
+        out = torch.full((p.W, p.Hq, p.S, p.Ev), float("nan"), dtype=p.dtype, device=dev)
+        bp = _cabi.bind(out=out, queries=d.queries, locations=d.locations, keys=d.keys, values=d.values, scale=p.scale,
+                        fragment_lengths=d.fragment_lengths, cos=d.cos, sin=d.sin, status=status)
+        need = _cabi.workspace_bytes(bp)
+        assert 0 < need <= 32 << 20
+        bp.struct.workspace, bp.struct.workspace_bytes = ptr, need
+        assert _cabi.launch(bp, stream) == 0
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0, name
+        check_against(out, golden[f"{name}/out"], p.dtype, what=name)
+
+
+def test_launch_shape_matches_what_runs():
+    p = wl.baseline_problem("target")
+    d = p.to("cuda:0")
+    out = torch.empty((p.W, p.Hq, p.S, p.Ev), dtype=p.dtype, device="cuda:0")
+    mk = lambda k: _cabi.bind(out=out, queries=d.queries, locations=d.locations, keys=d.keys, values=d.values,
+                              scale=p.scale, cos=d.cos, sin=d.sin, kernel=k)
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    shape = _cabi.launch_shape(mk(_cabi.KERNEL_MMA))
+    assert shape == dict(kernel=_cabi.KERNEL_MMA, ctas=sms, cluster=0, kernels_per_call=2)
+    shape = _cabi.launch_shape(mk(_cabi.KERNEL_MMA_CLUSTER))
+    assert shape["kernel"] == _cabi.KERNEL_MMA_CLUSTER and shape["kernels_per_call"] == 1
+    assert 2 <= shape["cluster"] <= 16 and shape["ctas"] == 8 * shape["cluster"] <= sms
+    # left to itself the library takes the persistent grid for this shape (67 MB of K/V) ...
+    assert _cabi.launch_shape(mk(_cabi.KERNEL_AUTO))["kernels_per_call"] == 2
+    # ... and clusters for half the context
+    half = wl.baseline_problem("target", lengths=[4096] + [1024] * 4).to("cuda:0")
+    bp = _cabi.bind(out=out, queries=half.queries, locations=half.locations, keys=half.keys, values=half.values,
+                    scale=half.scale, cos=half.cos, sin=half.sin)
+    assert _cabi.launch_shape(bp)["kernel"] == _cabi.KERNEL_MMA_CLUSTER
 
 
 def test_causal_chunk_config_matches_reference(golden):
@@ -56,7 +122,7 @@ def test_edge_cases_match_reference_on_every_eligible_kernel(golden, name):
 def test_result_does_not_depend_on_the_grid(golden, name, max_ctas):
     """Any number of CTAs cuts the tile list differently; the merged result must stay within tolerance."""
     p = wl.edge_problem(name)
-    for k in _kernels_for(p):
+    for k in _kernels_for(p, cluster=False):
         r = run_cabi(p, kernel=k, max_ctas=max_ctas)
         assert r.rc == 0 and r.status == 0
         check_against(r.out, golden[f"{name}/out"], p.dtype, what=f"{name} ctas {max_ctas} kernel {k}")
