@@ -259,6 +259,80 @@ int hogatt_copy_to_blocks_launch(const void* key_states, const void* value_state
                                  int32_t S_new, int32_t E, int32_t Ev, int32_t block_size, int32_t max_blocks,
                                  int32_t dtype, hogatt_stream_t stream);
 
+/* ---- the steps either side of the attention op in a decode step ------------------------------------- */
+
+/*
+ * Per-step metadata, on the device.  Every worker sees the same F fragments, each in its own order
+ * (shared prompt first, other workers' fragments, its own last); a new token's position with respect
+ * to fragment f is counted from the END of the worker's sequence: the fragment that comes last in the
+ * order ends at its own length, the one before it at the sum of both lengths, and so on, and token s
+ * of the S new ones sits at end - S + s.  Writes locations[f,w,s] (what hogatt_problem.locations takes)
+ * and the rotary tables for those positions, cos/sin[f,w,s,:] = cos/sin(position * inv_freq[i]) *
+ * attention_scaling with both halves equal (what hogatt_problem.cosines / sines take).
+ * A fragment that is missing from a worker's order gets location -1 (nothing visible).
+ * Replaces the layer-0 block of HogwildCache.update (python/hogwild/attention.py:164-204): Python loops
+ * over workers and fragments, torch.stack, and the model's rotary_emb, on every step.
+ */
+typedef struct hogatt_step_plan {
+    int32_t F, W, S, rotary_dim;
+    const int32_t* order;             /* device [W][F]: fragment ids in worker w's order, -1 after the last */
+    const int32_t* fragment_lengths;  /* device [F]: lengths INCLUDING the S tokens of this step            */
+    const float*   inv_freq;          /* device [rotary_dim / 2]                                            */
+    float   attention_scaling;        /* 1.0 for plain RoPE                                                 */
+    int32_t round_tables_to;          /* hogatt_dtype: HOGATT_F32 keeps the fp32 values; F16 / BF16 rounds
+                                         them to that type first, as rotary_emb does when it returns tables
+                                         in the model's type and the reference converts them back to float
+                                         (attention.py:191-193)                                             */
+    int32_t* locations;               /* out, device [F,W,S]                                                */
+    float*   cosines;                 /* out, device [F,W,S,rotary_dim] fp32                                */
+    float*   sines;
+} hogatt_step_plan;
+
+int hogatt_step_plan_launch(const hogatt_step_plan* p, hogatt_stream_t stream);
+
+/*
+ * K-side write path: rotate the new keys of every source at their own positions and append keys and
+ * values to the source's destination fragment, in place.  Fragments are preallocated slabs
+ * [Hkv, fragment_rows[f], E]: their pointers never change, the lengths live on the device.  Source w
+ * contributes its last (take_leading: first) new_rows[w] rows (all S when new_rows is NULL) at rows
+ * lengths_in[f] ... of fragment f = write_to[w]; sources that share a fragment follow each other in
+ * source order.  lengths_out[f] = lengths_in[f] + rows appended (a DIFFERENT buffer than lengths_in).
+ * Rows that do not fit into the slab are dropped and 256 is ORed into *device_status.
+ *   - table_dtype == HOGATT_F32: fp32 tables, products in fp32, one rounding to the tensors' type
+ *     (the arithmetic of hogwild_rope on queries);
+ *   - table_dtype == dtype: tables in the tensors' type, each product and the sum rounded to it -- what
+ *     torch computes in AttentionModule.forward, apply_rotary_pos_emb(key_states, cos, sin) with the
+ *     model's position_embeddings (python/hogwild/attention.py:84-90, :315).
+ * Replaces that call together with HogwildCache.update's write_to[w].update(...) (attention.py:148-158,
+ * a torch.cat per worker and layer) and, with one source whose table row is broadcast
+ * (table_strides = {0, 0}), the re-rotation loop of merge_caches (attention.py:251-257).
+ */
+#define HOGATT_MAX_APPEND_SOURCES 64
+typedef struct hogatt_append {
+    int32_t W, Hkv, E, Ev, S, rotary_dim, dtype, table_dtype;
+    const void* keys;              /* device; element (w, h, s, e) at keys + w*ks[0] + h*ks[1] + s*ks[2] + e   */
+    int64_t     key_strides[3];
+    const void* values;
+    int64_t     value_strides[3];
+    const void* cosines;           /* device; row (w, s) at cosines + w*ts[0] + s*ts[1], rotary_dim entries    */
+    const void* sines;
+    int64_t     table_strides[2];
+    const int32_t* new_rows;       /* device [W] or NULL                                                       */
+    const int32_t* write_to;       /* host [W]: destination fragment of every source                           */
+    int32_t F;
+    int32_t take_leading;          /* 0: new_rows counts from the END of a source (left-masked model input);
+                                      1: from its START (the source is itself a slab with new_rows valid rows,
+                                      as in merge_caches)                                                      */
+    void* const* key_fragments;    /* host array of F device pointers, [Hkv, fragment_rows[f], E]              */
+    void* const* value_fragments;  /* host array of F device pointers, [Hkv, fragment_rows[f], Ev]             */
+    const int32_t* fragment_rows;  /* host [F]: capacity of each slab in rows                                  */
+    const int32_t* lengths_in;     /* device [F]                                                               */
+    int32_t*       lengths_out;    /* device [F], not the same buffer as lengths_in                            */
+    int32_t*       device_status;  /* device int or NULL                                                       */
+} hogatt_append;
+
+int hogatt_append_launch(const hogatt_append* p, hogatt_stream_t stream);
+
 /*
  * Host-only description of how a problem is cut into work for the persistent grid; no GPU needed.
  * `visible_rows[f]` is the number of leading keys of fragment f that some query row can see.

@@ -20,7 +20,7 @@ MAX_FRAGMENTS = 128
 EXPORTS = ["hogatt_abi_version", "hogatt_status_string", "hogatt_last_cuda_error", "hogatt_workspace_bytes",
            "hogatt_sdpa_launch", "hogatt_fused_launch", "hogatt_fused_launch_static", "hogatt_fused_launch_gather", "hogatt_rope_launch",
            "hogatt_paged_workspace_bytes", "hogatt_paged_sdpa_launch", "hogatt_copy_to_blocks_launch", "hogatt_plan_describe",
-           "hogatt_plan_ranges", "hogatt_launch_shape"]
+           "hogatt_plan_ranges", "hogatt_launch_shape", "hogatt_step_plan_launch", "hogatt_append_launch"]
 
 
 class Problem(C.Structure):
@@ -85,6 +85,10 @@ def load() -> C.CDLL:
         lib.hogatt_paged_sdpa_launch.argtypes = [C.POINTER(PagedProblem), C.c_void_p]
         lib.hogatt_copy_to_blocks_launch.restype = C.c_int
         lib.hogatt_copy_to_blocks_launch.argtypes = [C.c_void_p] * 6 + [C.c_int32] * 8 + [C.c_void_p]
+        lib.hogatt_step_plan_launch.restype = C.c_int
+        lib.hogatt_step_plan_launch.argtypes = [C.POINTER(StepPlan), C.c_void_p]
+        lib.hogatt_append_launch.restype = C.c_int
+        lib.hogatt_append_launch.argtypes = [C.POINTER(Append), C.c_void_p]
         lib.hogatt_launch_shape.restype = C.c_int
         lib.hogatt_launch_shape.argtypes = [C.POINTER(Problem), C.POINTER(C.c_int32)]
         lib.hogatt_plan_describe.restype = C.c_int
@@ -110,6 +114,33 @@ def shape_problem(*, F, W, Hq, Hkv, E, Ev, S, dtype, rotary_dim=0, scale=1.0, ke
     p.F, p.W, p.Hq, p.Hkv, p.E, p.Ev, p.S = F, W, Hq, Hkv, E, Ev, S
     p.rotary_dim, p.dtype, p.scale, p.kernel, p.max_ctas = rotary_dim, dtype, scale, kernel, max_ctas
     return p
+
+
+class StepPlan(C.Structure):
+    _fields_ = [
+        ("F", C.c_int32), ("W", C.c_int32), ("S", C.c_int32), ("rotary_dim", C.c_int32),
+        ("order", C.c_void_p), ("fragment_lengths", C.c_void_p), ("inv_freq", C.c_void_p),
+        ("attention_scaling", C.c_float), ("round_tables_to", C.c_int32),
+        ("locations", C.c_void_p), ("cosines", C.c_void_p), ("sines", C.c_void_p),
+    ]
+
+
+MAX_APPEND_SOURCES = 64
+
+
+class Append(C.Structure):
+    _fields_ = [
+        ("W", C.c_int32), ("Hkv", C.c_int32), ("E", C.c_int32), ("Ev", C.c_int32), ("S", C.c_int32),
+        ("rotary_dim", C.c_int32), ("dtype", C.c_int32), ("table_dtype", C.c_int32),
+        ("keys", C.c_void_p), ("key_strides", C.c_int64 * 3),
+        ("values", C.c_void_p), ("value_strides", C.c_int64 * 3),
+        ("cosines", C.c_void_p), ("sines", C.c_void_p), ("table_strides", C.c_int64 * 2),
+        ("new_rows", C.c_void_p), ("write_to", C.POINTER(C.c_int32)),
+        ("F", C.c_int32), ("take_leading", C.c_int32),
+        ("key_fragments", C.POINTER(C.c_void_p)), ("value_fragments", C.POINTER(C.c_void_p)),
+        ("fragment_rows", C.POINTER(C.c_int32)),
+        ("lengths_in", C.c_void_p), ("lengths_out", C.c_void_p), ("device_status", C.c_void_p),
+    ]
 
 
 class BoundProblem:
@@ -210,3 +241,55 @@ def launch(bp: BoundProblem, stream: int = 0) -> int:
     lib = load()
     fn = lib.hogatt_fused_launch if bp.struct.cosines else lib.hogatt_sdpa_launch
     return int(fn(C.byref(bp.struct), C.c_void_p(stream)))
+
+
+def step_plan(*, order, fragment_lengths, inv_freq, S, locations, cosines, sines, attention_scaling=1.0,
+              round_tables_to=F32, stream: int = 0) -> int:
+    """``hogatt_step_plan_launch`` on torch CUDA tensors: ``order [W,F]`` int32, ``fragment_lengths [F]`` int32,
+    ``inv_freq [R/2]`` fp32; fills ``locations [F,W,S]`` int32 and ``cosines`` / ``sines [F,W,S,R]`` fp32."""
+    p = StepPlan()
+    W, F_ = order.shape
+    p.F, p.W, p.S, p.rotary_dim = F_, W, S, 2 * inv_freq.numel()
+    p.order, p.fragment_lengths, p.inv_freq = order.data_ptr(), fragment_lengths.data_ptr(), inv_freq.data_ptr()
+    p.attention_scaling, p.round_tables_to = float(attention_scaling), int(round_tables_to)
+    p.locations, p.cosines, p.sines = locations.data_ptr(), cosines.data_ptr(), sines.data_ptr()
+    return int(load().hogatt_step_plan_launch(C.byref(p), C.c_void_p(stream)))
+
+
+def append(*, keys, values, cosines, sines, write_to, key_fragments, value_fragments, lengths_in, lengths_out,
+           new_rows=None, take_leading=False, status=None, stream: int = 0) -> int:
+    """``hogatt_append_launch`` on torch CUDA tensors.  ``keys`` / ``values`` are ``[W,Hkv,S,E]`` views with any
+    strides whose last axis is contiguous; ``cosines`` / ``sines`` are ``[W,S,R]`` (or ``[1,1,R]`` / ``[R]`` to
+    broadcast one row), fp32 or the tensors' own type; fragments are ``[Hkv,capacity,E]`` slabs.  ``new_rows [W]``
+    int32 device: how many rows of each source are real, counted from its end (``take_leading``: from its start)."""
+    W, Hkv, S, E = keys.shape
+    Ev = values.shape[-1]
+    assert keys.stride(-1) == 1 and values.stride(-1) == 1 and cosines.stride(-1) == 1 and sines.stride(-1) == 1
+    p = Append()
+    p.W, p.Hkv, p.E, p.Ev, p.S = W, Hkv, E, Ev, S
+    p.rotary_dim, p.dtype, p.table_dtype = cosines.shape[-1], dtype_code(keys.dtype), dtype_code(cosines.dtype)
+    p.keys, p.values = keys.data_ptr(), values.data_ptr()
+    p.key_strides = (C.c_int64 * 3)(keys.stride(0), keys.stride(1), keys.stride(2))
+    p.value_strides = (C.c_int64 * 3)(values.stride(0), values.stride(1), values.stride(2))
+    p.cosines, p.sines = cosines.data_ptr(), sines.data_ptr()
+    if cosines.dim() == 3 and cosines.shape[0] == W and cosines.shape[1] == S:
+        ts = (cosines.stride(0), cosines.stride(1))
+        assert (sines.stride(0), sines.stride(1)) == ts
+    else:
+        assert cosines.numel() == cosines.shape[-1], "tables are [W,S,R] or a single row"
+        ts = (0, 0)
+    p.table_strides = (C.c_int64 * 2)(*ts)
+    p.new_rows = new_rows.data_ptr() if new_rows is not None else None
+    p.take_leading = 1 if take_leading else 0
+    wt = (C.c_int32 * W)(*[int(x) for x in write_to])
+    p.write_to = C.cast(wt, C.POINTER(C.c_int32))
+    F_ = len(key_fragments)
+    kp = (C.c_void_p * F_)(*[k.data_ptr() for k in key_fragments])
+    vp = (C.c_void_p * F_)(*[v.data_ptr() for v in value_fragments])
+    rows = (C.c_int32 * F_)(*[int(k.shape[-2]) for k in key_fragments])
+    p.F = F_
+    p.key_fragments, p.value_fragments = C.cast(kp, C.POINTER(C.c_void_p)), C.cast(vp, C.POINTER(C.c_void_p))
+    p.fragment_rows = C.cast(rows, C.POINTER(C.c_int32))
+    p.lengths_in, p.lengths_out = lengths_in.data_ptr(), lengths_out.data_ptr()
+    p.device_status = status.data_ptr() if status is not None else None
+    return int(load().hogatt_append_launch(C.byref(p), C.c_void_p(stream)))

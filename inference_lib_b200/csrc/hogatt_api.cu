@@ -11,6 +11,7 @@
 #include "hogatt_merge.cuh"
 #include "hogatt_mma.cuh"
 #include "hogatt_paged.cuh"
+#include "hogatt_cache.cuh"
 
 namespace hogatt {
 namespace {
@@ -297,7 +298,7 @@ int choose_cluster(const hogatt_problem* p, const Resolved& r, int dev, int sms,
 // cluster >= 2: units * cluster CTAs in clusters of `cluster`; the kernel merges by itself.
 template <class T, int HD, int MT>
 int launch_mma(const KernelArgs& args, int F, int dev, int smem_optin, int grid, int cluster, bool evict_first,
-               cudaStream_t stream) {
+               cudaStream_t stream, int extra_flags = 0) {
     using C = MmaCfg<HD, MT>;
     const size_t smem = mma_smem_bytes<HD, MT>(F);
     if (smem > (size_t)smem_optin) return HOGATT_ERR_TOO_MANY_FRAGMENTS;
@@ -306,7 +307,7 @@ int launch_mma(const KernelArgs& args, int F, int dev, int smem_optin, int grid,
         int rc = ensure_smem_limit(mma_attention_kernel<T, HD, MT, false>, dev, smem, granted);
         if (rc != HOGATT_OK) return rc;
         HOGATT_CUDA_OK(launch_kernel(mma_attention_kernel<T, HD, MT, false>, dim3(grid), dim3(C::THREADS), smem, stream,
-                                     args, evict_first ? 1 : 0));
+                                     args, (evict_first ? 1 : 0) | extra_flags));
         return HOGATT_OK;
     }
     // the wide-cluster opt-in was set when choose_cluster() asked for the residency; the shared-memory limit
@@ -327,21 +328,21 @@ int launch_mma(const KernelArgs& args, int F, int dev, int smem_optin, int grid,
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled() ? 2 : 1;
-    HOGATT_CUDA_OK(cudaLaunchKernelEx(&cfg, mma_attention_kernel<T, HD, MT, true>, args, (int)(evict_first ? 1 : 0)));
+    HOGATT_CUDA_OK(cudaLaunchKernelEx(&cfg, mma_attention_kernel<T, HD, MT, true>, args, (int)((evict_first ? 1 : 0) | extra_flags)));
     return HOGATT_OK;
 }
 
 template <class T>
 int launch_mma_dims(const KernelArgs& args, int F, int HD, int MT, int dev, int smem_optin, int grid, int cluster, bool ef,
-                    cudaStream_t stream) {
+                    cudaStream_t stream, int extra_flags = 0) {
     if (HD == 128) {
-        if (MT == 1) return launch_mma<T, 128, 1>(args, F, dev, smem_optin, grid, cluster, ef, stream);
-        if (MT == 2) return launch_mma<T, 128, 2>(args, F, dev, smem_optin, grid, cluster, ef, stream);
-        return launch_mma<T, 128, 4>(args, F, dev, smem_optin, grid, cluster, ef, stream);
+        if (MT == 1) return launch_mma<T, 128, 1>(args, F, dev, smem_optin, grid, cluster, ef, stream, extra_flags);
+        if (MT == 2) return launch_mma<T, 128, 2>(args, F, dev, smem_optin, grid, cluster, ef, stream, extra_flags);
+        return launch_mma<T, 128, 4>(args, F, dev, smem_optin, grid, cluster, ef, stream, extra_flags);
     }
-    if (MT == 1) return launch_mma<T, 64, 1>(args, F, dev, smem_optin, grid, cluster, ef, stream);
-    if (MT == 2) return launch_mma<T, 64, 2>(args, F, dev, smem_optin, grid, cluster, ef, stream);
-    return launch_mma<T, 64, 4>(args, F, dev, smem_optin, grid, cluster, ef, stream);
+    if (MT == 1) return launch_mma<T, 64, 1>(args, F, dev, smem_optin, grid, cluster, ef, stream, extra_flags);
+    if (MT == 2) return launch_mma<T, 64, 2>(args, F, dev, smem_optin, grid, cluster, ef, stream, extra_flags);
+    return launch_mma<T, 64, 4>(args, F, dev, smem_optin, grid, cluster, ef, stream, extra_flags);
 }
 
 template <class T, int EV>
@@ -370,7 +371,11 @@ template <class T>
 int launch_all(const KernelArgs& args, const Resolved& r, int dev, int smem_optin, int grid, cudaStream_t stream) {
     int rc;
     if (r.kernel == HOGATT_KERNEL_MMA) {
-        const bool ef = r.row_blocks == 1;       // every K/V byte is read once: do not let it displace L2 contents
+        bool ef = r.row_blocks == 1;             // every K/V byte is read once: do not let it displace L2 contents
+#ifdef HOGATT_EXPERIMENT
+        if (getenv("HOGATT_STREAM_ONLY")) return launch_mma_dims<T>(args, args.F, args.E, r.mt, dev, smem_optin,
+                                                                    r.cluster > 1 ? r.units * r.cluster : grid, r.cluster, ef, stream, 2);
+#endif
         if (r.cluster > 1)      // the cluster kernel merges by itself
             return launch_mma_dims<T>(args, args.F, args.E, r.mt, dev, smem_optin, r.units * r.cluster, r.cluster, ef, stream);
         rc = launch_mma_dims<T>(args, args.F, args.E, r.mt, dev, smem_optin, grid, 0, ef, stream);
@@ -789,6 +794,81 @@ int hogatt_plan_describe(const hogatt_problem* p, const int32_t* visible_rows, i
     plan[5] = cluster ? r.units * cluster : effective_ctas((int64_t)r.units * th, grid);
     plan[6] = cluster ? cluster : max_parts_per_unit(r.units, grid);
     plan[7] = cluster ? HOGATT_KERNEL_MMA_CLUSTER : r.kernel;
+    return HOGATT_OK;
+}
+
+int hogatt_step_plan_launch(const hogatt_step_plan* p, hogatt_stream_t stream) {
+    if (!p) return HOGATT_ERR_NULL_POINTER;
+    if (!p->order || !p->fragment_lengths || !p->inv_freq || !p->locations || !p->cosines || !p->sines)
+        return HOGATT_ERR_NULL_POINTER;
+    if (p->F <= 0 || p->W <= 0 || p->S <= 0 || p->rotary_dim <= 0 || (p->rotary_dim & 1)) return HOGATT_ERR_BAD_SHAPE;
+    if (p->F > HOGATT_MAX_FRAGMENTS) return HOGATT_ERR_TOO_MANY_FRAGMENTS;
+    if ((int64_t)p->F * p->W > (1 << 24) || (int64_t)p->F * p->W * p->S > (1 << 26)) return HOGATT_ERR_TOO_LARGE;
+    if (p->round_tables_to != HOGATT_F32 && p->round_tables_to != HOGATT_F16 && p->round_tables_to != HOGATT_BF16)
+        return HOGATT_ERR_UNSUPPORTED_DTYPE;
+    StepPlanArgs a;
+    a.F = p->F; a.W = p->W; a.S = p->S; a.R = p->rotary_dim;
+    a.order = p->order; a.lengths = p->fragment_lengths; a.inv_freq = p->inv_freq;
+    a.attention_scaling = p->attention_scaling;
+    a.round_to = p->round_tables_to;
+    a.loc = p->locations; a.cos = p->cosines; a.sin = p->sines;
+    step_plan_kernel<<<(unsigned)(p->F * p->W), 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(a);
+    HOGATT_CUDA_OK(cudaGetLastError());
+    return HOGATT_OK;
+}
+
+int hogatt_append_launch(const hogatt_append* p, hogatt_stream_t stream) {
+    if (!p) return HOGATT_ERR_NULL_POINTER;
+    if (!p->keys || !p->values || !p->cosines || !p->sines || !p->write_to || !p->key_fragments || !p->value_fragments ||
+        !p->fragment_rows || !p->lengths_in || !p->lengths_out)
+        return HOGATT_ERR_NULL_POINTER;
+    if (p->lengths_in == p->lengths_out) return HOGATT_ERR_BAD_SHAPE;
+    if (p->W <= 0 || p->W > HOGATT_MAX_APPEND_SOURCES || p->Hkv <= 0 || p->E <= 0 || p->Ev <= 0 || p->S <= 0 || p->F <= 0 ||
+        p->rotary_dim <= 0 || p->rotary_dim > p->E || (p->rotary_dim & 1))
+        return HOGATT_ERR_BAD_SHAPE;
+    if (p->F > HOGATT_MAX_FRAGMENTS) return HOGATT_ERR_TOO_MANY_FRAGMENTS;
+    if (p->dtype != HOGATT_F32 && p->dtype != HOGATT_F16 && p->dtype != HOGATT_BF16) return HOGATT_ERR_UNSUPPORTED_DTYPE;
+    if (p->table_dtype != HOGATT_F32 && p->table_dtype != p->dtype) return HOGATT_ERR_UNSUPPORTED_DTYPE;
+    AppendArgs a;
+    memset(&a, 0, sizeof(a));
+    a.W = p->W; a.Hkv = p->Hkv; a.E = p->E; a.Ev = p->Ev; a.S = p->S; a.R = p->rotary_dim; a.F = p->F;
+    a.tables_lowp = (p->table_dtype != HOGATT_F32) ? 1 : 0;
+    a.take_leading = p->take_leading ? 1 : 0;
+    a.k = p->keys; a.v = p->values; a.cos = p->cosines; a.sin = p->sines;
+    for (int i = 0; i < 3; ++i) {
+        a.ks[i] = p->key_strides[i];
+        a.vs[i] = p->value_strides[i];
+    }
+    a.ts[0] = p->table_strides[0]; a.ts[1] = p->table_strides[1];
+    a.new_rows = p->new_rows; a.len_in = p->lengths_in; a.len_out = p->lengths_out; a.status = p->device_status;
+    for (int w = 0; w < p->W; ++w) {
+        if (p->write_to[w] < 0 || p->write_to[w] >= p->F) return HOGATT_ERR_BAD_SHAPE;
+        a.write_to[w] = p->write_to[w];
+    }
+    const size_t sz = dtype_size(p->dtype);
+    const int vec = 16 / (int)sz;
+    bool vectorised = sz == 2 && p->E % vec == 0 && p->Ev % vec == 0 && aligned16(p->keys) && aligned16(p->values);
+    for (int i = 0; i < 3; ++i) vectorised = vectorised && p->key_strides[i] % vec == 0 && p->value_strides[i] % vec == 0;
+    if (!a.tables_lowp)           // rotate_chunk reads the fp32 tables eight entries at a time, both halves of the rotation
+        vectorised = vectorised && p->rotary_dim % 16 == 0 && aligned16(p->cosines) && aligned16(p->sines) &&
+                     p->table_strides[0] % 4 == 0 && p->table_strides[1] % 4 == 0;
+    for (int f = 0; f < p->F; ++f) {
+        if (p->fragment_rows[f] < 0) return HOGATT_ERR_BAD_SHAPE;
+        if (p->fragment_rows[f] > 0 && (!p->key_fragments[f] || !p->value_fragments[f])) return HOGATT_ERR_NULL_POINTER;
+        if (!aligned16(p->key_fragments[f]) || !aligned16(p->value_fragments[f])) return HOGATT_ERR_MISALIGNED;
+        a.ft.e[f].k = p->key_fragments[f];
+        a.ft.e[f].v = p->value_fragments[f];
+        a.ft.e[f].rows = p->fragment_rows[f];
+    }
+    const int64_t pieces = (int64_t)p->S * ((p->E + p->Ev) / (vectorised ? vec : 1));
+    dim3 grid((unsigned)std::min<int64_t>((pieces + 255) / 256, 1 << 14), (unsigned)p->Hkv, (unsigned)p->W);
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    switch (p->dtype) {
+        case HOGATT_F32: append_kernel<float><<<grid, 256, 0, st>>>(a, 0); break;
+        case HOGATT_F16: append_kernel<__half><<<grid, 256, 0, st>>>(a, vectorised ? 1 : 0); break;
+        default: append_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(a, vectorised ? 1 : 0); break;
+    }
+    HOGATT_CUDA_OK(cudaGetLastError());
     return HOGATT_OK;
 }
 

@@ -39,6 +39,9 @@ struct MmaCfg {
     // consumer warps.  Up to 8 warps per CTA may use 255 registers each; from the 9th on the register
     // file only gives 168, which spills the accumulators -- so two m-tiles run on 4 warps (two key
     // slices each) rather than 8.
+    // consumer warps.  Up to 8 warps per CTA may use 255 registers each; beyond that the register file only
+    // gives 168, which spills the accumulators -- so one or two m-tiles run on 4 warps (four or two key
+    // slices each).  (8 consumer warps for every shape were measured: 2-4 us slower per call.)
     static constexpr int NCW = (MT == 4) ? 8 : 4;
     static constexpr int NSLICE = NCW / MT;              // warps sharing one m-tile, each takes a slice of the keys
     static constexpr int GT = (HD == 128) ? 16 : 32;     // keys per group (one 4 KiB bulk copy)
@@ -51,7 +54,13 @@ struct MmaCfg {
     static constexpr int NT_S = GT / NSLICE;             // 8-key n-tiles per warp per stage
     static constexpr int NT_O = HD / 8;                  // output n-tiles
     static constexpr int KSTEPS = HD / 16;
-    static constexpr int THREADS = (NCW + 1) * 32;
+    // Producer warps: warp 0, and with NPW == 2 also warp NCW + 1 (then warp 0 copies the K half of a tile,
+    // the other the V half).  Issuing one bulk copy costs the issuing warp ~55 ns whatever its size, so one
+    // producer needs 0.88 us for the 16 copies of a stage, which caps one SM at 74 GB/s; two producers lift
+    // that to ~100 GB/s per SM.  With a CTA on every SM the chip's HBM gives each SM 44 GB/s, and the
+    // second producer measured 0.5-1 us SLOWER per call there; it only pays when few SMs stream a lot.
+    static constexpr int NPW = 1;
+    static constexpr int THREADS = (NCW + NPW) * 32;
     static constexpr int RPB = 16 * MT;                  // query rows per CTA
     static constexpr int SLOT_FLOATS = NT_O * 4 * 32;    // one warp's accumulators
     static constexpr int QPITCH = ROWB + 16;             // bytes per staged query row (padding: conflict-free ldmatrix)
@@ -134,7 +143,7 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
 
     if (tid == 0) {
         for (int s = 0; s < C::NSTAGE; ++s) {
-            mbar_init(full0 + 8 * s, 1);
+            mbar_init(full0 + 8 * s, C::NPW);
             mbar_init(empty0 + 8 * s, C::NCW);
         }
         mbar_init(cbar, C::NCW);
@@ -160,7 +169,7 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
     // it after their first fragment prologue, while the first K/V tile is still in flight.
     const bool want_rq = a.rq != nullptr && a.cos != nullptr;
     if ((int)blockIdx.x >= ctas) {
-        if (want_rq && warp > 0)
+        if (want_rq && warp > 0 && warp <= C::NCW)
             write_rotated_queries<T>(a.q, a.rq, a.cos, a.sin, a.F, a.W, a.Hq, a.S, HD, a.R,
                                      blockIdx.x * (C::NCW * 32) + tid - 32, gridDim.x * (C::NCW * 32));
         return;
@@ -180,9 +189,11 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
     // =====================================================================================
     // Producer warp
     // =====================================================================================
-    if (warp == 0) {
+    if (warp == 0 || warp > C::NCW) {
+        constexpr int COPIES = 16 / C::NPW;              // bulk copies per producer warp per stage (8 K groups + 8 V groups in all)
+        const int copy0 = warp == 0 ? 0 : COPIES;
         uint64_t policy = 0;
-        if (use_evict_first) policy = l2_policy_evict_first();
+        if (use_evict_first & 1) policy = l2_policy_evict_first();
         int64_t u = CL ? (int64_t)(blockIdx.x / CS) : t0 / TH;
         int j = (int)(t0 - u * TH), fscan = 0, it = 0;
         bool ok = true;
@@ -198,17 +209,17 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             const uint32_t fullb = full0 + 8 * stage;
-            if (lane == 0) mbar_arrive_expect_tx(fullb, (uint32_t)ntok * C::ROWB * 2u);
+            if (lane == 0) mbar_arrive_expect_tx(fullb, (uint32_t)ntok * C::ROWB * (2u / C::NPW));
             __syncwarp();
-            if (lane < 16) {
-                const int g = lane & 7;
+            if (lane < COPIES) {
+                const int g = (copy0 + lane) & 7;
+                const bool is_v = copy0 + lane >= 8;
                 const int tg = min(C::GT, ntok - g * C::GT);
                 if (tg > 0) {
-                    const bool is_v = lane >= 8;
                     const unsigned char* src = static_cast<const unsigned char*>(is_v ? a.ft.e[f].v : a.ft.e[f].k) +
                                                ((size_t)hkv * a.ft.e[f].rows + tok0 + g * C::GT) * C::ROWB;
                     const uint32_t dst = stage0 + stage * C::STAGE_BYTES + (is_v ? C::KV_BYTES : 0) + g * C::GROUP_STRIDE;
-                    if (use_evict_first)
+                    if (use_evict_first & 1)
                         bulk_load_hint(dst, src, (uint32_t)tg * C::ROWB, fullb, policy);
                     else
                         bulk_load(dst, src, (uint32_t)tg * C::ROWB, fullb);
@@ -295,8 +306,8 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
             if (warp == 1) HOGATT_TL(1, 20);
             {
                 constexpr int CPR = HD / 8;                                    // 16-byte chunks per row
-                constexpr int ITEMS = C::RPB * CPR / (C::NCW * 32);            // chunks per thread
-                static_assert(ITEMS * C::NCW * 32 == C::RPB * CPR, "chunks must divide evenly over the consumer threads");
+                constexpr int NCHUNK = C::RPB * CPR;
+                constexpr int ITEMS = (NCHUNK + C::NCW * 32 - 1) / (C::NCW * 32);   // chunks per thread
                 const bool chunked = a.cos == nullptr || chunked_rope_ok(a.cos, a.sin, a.R, HD);
                 const int ctid = tid - 32;
                 uint4 val[ITEMS];
@@ -306,7 +317,7 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
                     const int item = ctid + k * (C::NCW * 32);
                     const int r = item / CPR, ch = item % CPR;
                     const int gr = rb * C::RPB + r;
-                    live[k] = gr < a.rows_total;
+                    live[k] = item < NCHUNK && gr < a.rows_total;
                     const RowId id = decode_row(live[k] ? gr : 0, a.G, a.S);
                     const int hq = hkv * a.G + id.g;
                     if (a.cos == nullptr) {
@@ -330,7 +341,8 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
                 for (int k = 0; k < ITEMS; ++k) {
                     const int item = ctid + k * (C::NCW * 32);
                     const int r = item / CPR, ch = item % CPR;
-                    *reinterpret_cast<uint4*>(qtile + r * C::QPITCH + ch * 16) = live[k] ? val[k] : make_uint4(0u, 0u, 0u, 0u);
+                    if (item < NCHUNK)
+                        *reinterpret_cast<uint4*>(qtile + r * C::QPITCH + ch * 16) = live[k] ? val[k] : make_uint4(0u, 0u, 0u, 0u);
                 }
             }
             if (warp == 1) HOGATT_TL(1, 21);
@@ -361,6 +373,17 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
         if (warp == 1) HOGATT_TL(1, 100 + it);
 #ifdef HOGATT_TIMELINE
         if (warp == 1 && lane == 0 && it == 0) g_cta_t[1][blockIdx.x] = global_timer_ns_();
+#endif
+#ifdef HOGATT_EXPERIMENT
+        if (use_evict_first & 2) {           // stream only: hand the stage straight back (results are garbage)
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty0 + 8 * stage);
+            if (++j == TH) {
+                j = 0;
+                ++u;
+            }
+            continue;
+        }
 #endif
 
         const int i0 = slice * C::NT_S;      // first in-group position of this warp's slice
@@ -581,7 +604,7 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
         if (warp == 1) HOGATT_TL(1, 901);
 
         // ---- merge rows crank, crank + CS, ... of the block over every warp of every CTA ----
-        const int P = CS * C::NSLICE;                     // partials per row (<= 64)
+        const int P = CS * C::NSLICE;                     // partials per row (<= 128)
         const int RC = (C::RPB - crank + CS - 1) / CS;    // rows this CTA finishes (CS <= 16 <= RPB: at least one)
         const int SPLIT = max(1, C::NCW / ((C::RPB + CS - 1) / CS));   // warps sharing one row, each takes partials p % SPLIT == sub
         const int ntask = RC * SPLIT;
@@ -590,9 +613,9 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
             const int ri = task / SPLIT, sub = task % SPLIT;
             const int r = crank + ri * CS;
             const int mt_r = r >> 4, rr = r & 15;
-            float mp[2], lp[2];
+            float mp[4], lp[4];
 #pragma unroll
-            for (int k = 0; k < 2; ++k) {
+            for (int k = 0; k < 4; ++k) {
                 const int p = lane + 32 * k;
                 mp[k] = -INFINITY;
                 lp[k] = 0.f;
@@ -603,12 +626,12 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
                     lp[k] = ld_cluster_f(ad + C::NCW * 16 * 4);
                 }
             }
-            float M = fmaxf(mp[0], mp[1]);
+            float M = fmaxf(fmaxf(mp[0], mp[1]), fmaxf(mp[2], mp[3]));
 #pragma unroll
             for (int sh = 16; sh > 0; sh >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, sh));
             const float mu = (M == -INFINITY) ? 0.f : M;
-            const float w0 = exp2f(mp[0] - mu), w1 = exp2f(mp[1] - mu);
-            float den = lp[0] * w0 + lp[1] * w1;
+            const float w0 = exp2f(mp[0] - mu), w1 = exp2f(mp[1] - mu), w2 = exp2f(mp[2] - mu), w3 = exp2f(mp[3] - mu);
+            float den = lp[0] * w0 + lp[1] * w1 + lp[2] * w2 + lp[3] * w3;
 #pragma unroll
             for (int sh = 16; sh > 0; sh >>= 1) den += __shfl_xor_sync(0xffffffffu, den, sh);
             const bool act = lane * 4 < HD;
@@ -629,7 +652,8 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
 #pragma unroll
                 for (int i = 0; i < UNR; ++i) {
                     const int p = p0 + i * SPLIT;
-                    const float wgt = __shfl_sync(0xffffffffu, (p & 32) ? w1 : w0, p & 31);
+                    const int hi = (p >> 5) & 3;
+                    const float wgt = __shfl_sync(0xffffffffu, hi == 0 ? w0 : (hi == 1 ? w1 : (hi == 2 ? w2 : w3)), p & 31);
                     acc.x = fmaf(x[i].x, wgt, acc.x);
                     acc.y = fmaf(x[i].y, wgt, acc.y);
                     acc.z = fmaf(x[i].z, wgt, acc.z);
