@@ -1,6 +1,9 @@
 // Tensor-core fragment attention for fp16 / bf16 with E == Ev in {64, 128}: the hot path.
 //
-// One persistent CTA per SM walks a contiguous range of KV tiles (see hogatt_plan.h).
+// Two launch shapes of one kernel (template parameter CL, see the comment above the kernel): a persistent
+// grid, one CTA per SM walking a contiguous range of KV tiles (hogatt_plan.h), partial results merged by
+// merge_kernel; or thread-block clusters, one per (kv head, row block) unit, which merge by themselves
+// through distributed shared memory.  Inside a CTA both are the same:
 //   * warp 0 is the producer: it streams K and V tiles global -> shared with 1-D bulk async
 //     copies (TMA engine) into a ring of NSTAGE stages, completion counted on mbarriers.  A tile
 //     is a run of consecutive keys of one fragment and one
@@ -36,9 +39,6 @@ namespace hogatt {
 
 template <int HD, int MT>
 struct MmaCfg {
-    // consumer warps.  Up to 8 warps per CTA may use 255 registers each; from the 9th on the register
-    // file only gives 168, which spills the accumulators -- so two m-tiles run on 4 warps (two key
-    // slices each) rather than 8.
     // consumer warps.  Up to 8 warps per CTA may use 255 registers each; beyond that the register file only
     // gives 168, which spills the accumulators -- so one or two m-tiles run on 4 warps (four or two key
     // slices each).  (8 consumer warps for every shape were measured: 2-4 us slower per call.)
