@@ -276,9 +276,12 @@ int mma_best_cluster_dims(int HD, int MT, int dev, int F, int smem_optin, int un
 // and the second launch, but it only uses units * cluster SMs and one SM pulls about 66 GB/s: it wins
 // where the fixed costs dominate.  Fitted to measurements on B200 at 8 kv heads (us per call, B bytes
 // streamed, n CTAs; beyond 64 CTAs -- clusters of 10 -- the cluster shape did not get faster):
-//   persistent grid ~ 11.4 + B / 6.07 TB/s        cluster ~ 8.5 + B / (min(n, 64) * 66 GB/s)
-// i.e. the cluster shape below about 40 MB per call (8K keys at 8 kv heads of 128), the persistent grid above.
-constexpr double kPersistFixedUs = 11.4, kClusterFixedUs = 8.5, kChipBytesPerUs = 6.07e6, kSmBytesPerUs = 66e3;
+//   persistent grid ~ 10.0 + 0.045 * partials per unit + B / 6.07 TB/s     (10.8 at 8 kv heads: 18.5 CTAs each)
+//   cluster         ~ 8.5 + B / (min(n, 64) * 66 GB/s)
+// i.e. the cluster shape below about 32 MB per call at 8 kv heads, the persistent grid above; with fewer kv
+// heads per GPU (sharded) the persistent grid has more partials per head to merge and the crossover moves up.
+constexpr double kPersistFixedUs = 10.0, kPersistPerPartUs = 0.045, kClusterFixedUs = 8.5, kChipBytesPerUs = 6.07e6,
+                 kSmBytesPerUs = 66e3;
 constexpr int kClusterUsefulCtas = 64;
 int choose_cluster(const hogatt_problem* p, const Resolved& r, int dev, int sms, int smem_optin, int64_t tiles_per_unit) {
     if (r.kernel != HOGATT_KERNEL_MMA || r.cluster_mode < 0 || 2 * r.units > sms) return 0;
@@ -289,7 +292,7 @@ int choose_cluster(const hogatt_problem* p, const Resolved& r, int dev, int sms,
     if (p->max_ctas > 0) return 0;                       // the caller is testing grid sizes of the persistent variant
     cs = std::min(cs, std::max(2, kClusterUsefulCtas / r.units));
     const double bytes = (double)tiles_per_unit * r.units * MmaCfg<128, 1>::STAGE_BYTES;
-    const double persistent = kPersistFixedUs + bytes / kChipBytesPerUs;
+    const double persistent = kPersistFixedUs + kPersistPerPartUs * sms / r.units + bytes / kChipBytesPerUs;
     const double cluster = kClusterFixedUs + bytes / (kSmBytesPerUs * std::min(r.units * cs, kClusterUsefulCtas));
     return cluster < persistent ? cs : 0;
 }

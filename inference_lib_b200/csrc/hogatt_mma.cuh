@@ -65,6 +65,13 @@ struct MmaCfg {
     static constexpr int SLOT_FLOATS = NT_O * 4 * 32;    // one warp's accumulators
     static constexpr int QPITCH = ROWB + 16;             // bytes per staged query row (padding: conflict-free ldmatrix)
     static constexpr int QBYTES = RPB * QPITCH;
+    // Second query tile (+ one visibility limit per row): a CTA whose tile range runs on into a second fragment
+    // or unit stages that segment's rotated queries at kernel start too, while ordinary loads still take one
+    // quick round trip -- in the middle of the stream they queue behind megabytes of bulk copies.  Where the
+    // Only for 16-row blocks: with 32 rows the extra state pushed the streaming loop into register spills
+    // (+0.3 us measured), with 64 rows the shared memory has no room for it; those stage every segment when
+    // it is reached.
+    static constexpr int Q2BYTES = (MT == 1) ? QBYTES + RPB * 4 : 0;
     // cluster variant: what a CTA leaves in its own shared memory for the cluster-wide merge
     static constexpr int OPITCH = HD + 8;                // floats per partial row (padding: conflict-free float2 stores)
     static constexpr int CL_PART_FLOATS = 16 * OPITCH;   // one warp's 16 rows
@@ -81,7 +88,7 @@ struct MmaCfg {
 template <int HD, int MT>
 __host__ __device__ inline size_t mma_smem_bytes(int F) {
     using C = MmaCfg<HD, MT>;
-    return 128 /* alignment slack */ + (size_t)C::NSTAGE * C::STAGE_BYTES + C::QBYTES +
+    return 128 /* alignment slack */ + (size_t)C::NSTAGE * C::STAGE_BYTES + C::QBYTES + C::Q2BYTES +
            (size_t)C::NCW * 32 * 4 * 4 /* stats */ + (2 * C::NSTAGE + 1) * 8 /* barriers */ + 16 /* abort flag */ +
            ((size_t)2 * F + 1) * 4;
 }
@@ -120,7 +127,8 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
     unsigned char* base = reinterpret_cast<unsigned char*>(((uintptr_t)smem_dyn + 127) & ~(uintptr_t)127);
     unsigned char* stages = base;
     unsigned char* qtile = stages + (size_t)C::NSTAGE * C::STAGE_BYTES;                     // [RPB][QPITCH]
-    float* stats = reinterpret_cast<float*>(qtile + C::QBYTES);                             // [NCW][32][4]
+    unsigned char* qtile2 = qtile + C::QBYTES;                                              // [RPB][QPITCH] + int[RPB]
+    float* stats = reinterpret_cast<float*>(qtile2 + C::Q2BYTES);                           // [NCW][32][4]
     uint64_t* bars = reinterpret_cast<uint64_t*>(stats + C::NCW * 32 * 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * C::NSTAGE + 1);
     int* vis = const_cast<int*>(abort_flag) + 4;
@@ -274,6 +282,7 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
 
     int64_t u = CL ? (int64_t)(blockIdx.x / CS) : t0 / TH;
     int j = (int)(t0 - u * TH), fscan = 0, it = 0, cur_u = -1, cur_f = -1, hkv = 0, rb = 0;
+    int pre_u = -1, pre_f = -1;          // the segment whose queries sit in the second tile
     for (int64_t t = t0; t < t1; ++t, ++it) {
         if ((int)u != cur_u) {
             cur_u = (int)u;
@@ -300,62 +309,105 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
             // every load independent: one memory round trip), round them to the storage type and
             // stage them in shared memory; each warp then pulls its MMA A-fragments with ldmatrix.
             const int vf = vis[f];
-            const int loc_a = valid_a ? a.loc[(f * a.W + id_a.w) * a.S + id_a.s] : vf;
-            const int loc_b = valid_b ? a.loc[(f * a.W + id_b.w) * a.S + id_b.s] : vf;
-            if (!consumer_sync()) break;                       // everyone is done with the previous query tile
-            if (warp == 1) HOGATT_TL(1, 20);
-            {
-                constexpr int CPR = HD / 8;                                    // 16-byte chunks per row
-                constexpr int NCHUNK = C::RPB * CPR;
-                constexpr int ITEMS = (NCHUNK + C::NCW * 32 - 1) / (C::NCW * 32);   // chunks per thread
-                const bool chunked = a.cos == nullptr || chunked_rope_ok(a.cos, a.sin, a.R, HD);
-                const int ctid = tid - 32;
-                uint4 val[ITEMS];
-                bool live[ITEMS];
-#pragma unroll
-                for (int k = 0; k < ITEMS; ++k) {              // all loads of all chunks are issued before any is used
-                    const int item = ctid + k * (C::NCW * 32);
-                    const int r = item / CPR, ch = item % CPR;
-                    const int gr = rb * C::RPB + r;
-                    live[k] = item < NCHUNK && gr < a.rows_total;
-                    const RowId id = decode_row(live[k] ? gr : 0, a.G, a.S);
-                    const int hq = hkv * a.G + id.g;
-                    if (a.cos == nullptr) {
-                        val[k] = *reinterpret_cast<const uint4*>(
-                            q + ((size_t)((f * a.W + id.w) * a.Hq + hq) * a.S + id.s) * HD + ch * 8);
-                    } else {
-                        const T* qrow = q + ((size_t)(id.w * a.Hq + hq) * a.S + id.s) * HD;
-                        const size_t tab = ((size_t)(f * a.W + id.w) * a.S + id.s) * a.R;
-                        if (chunked) {
-                            val[k] = rotate_chunk<T>(qrow, a.cos + tab, a.sin + tab, ch, a.R);
-                        } else {
-                            uint32_t* o32 = reinterpret_cast<uint32_t*>(&val[k]);
-#pragma unroll
-                            for (int c = 0; c < 4; ++c)
-                                o32[c] = pack2<T>(rope_channel<T>(qrow, a.cos + tab, a.sin + tab, ch * 8 + 2 * c, a.R),
-                                                  rope_channel<T>(qrow, a.cos + tab, a.sin + tab, ch * 8 + 2 * c + 1, a.R));
+            const unsigned char* qsrc = qtile;
+            if (C::Q2BYTES != 0 && pre_u == cur_u && pre_f == f) {
+                // staged at kernel start: nothing to load (the tile has been complete since the second
+                // barrier of the first prologue, and nobody writes it again)
+                const int* qlim2 = reinterpret_cast<const int*>(qtile2 + C::QBYTES);
+                qsrc = qtile2;
+                lim_a = qlim2[row_a];
+                lim_b = qlim2[row_b];
+                pre_u = -1;
+            } else {
+                const int loc_a = valid_a ? a.loc[(f * a.W + id_a.w) * a.S + id_a.s] : vf;
+                const int loc_b = valid_b ? a.loc[(f * a.W + id_b.w) * a.S + id_b.s] : vf;
+                // the segment after this one, if the CTA's range reaches it (first prologue only)
+                int nseg = 1, u2 = 0, f2 = 0;
+                if (C::Q2BYTES != 0 && it == 0) {
+                    const int64_t seg_end = u * TH + pre[f + 1];
+                    if (seg_end < t1) {
+                        int j2 = pre[f + 1];
+                        u2 = cur_u;
+                        if (j2 >= TH) {
+                            j2 = 0;
+                            ++u2;
                         }
+                        f2 = 0;
+                        while (j2 >= pre[f2 + 1]) ++f2;
+                        nseg = 2;
+                        pre_u = u2;
+                        pre_f = f2;
                     }
                 }
+                if (!consumer_sync()) break;                   // everyone is done with the previous query tile
+                if (warp == 1) HOGATT_TL(1, 20);
+#pragma unroll 1
+                for (int seg = 0; seg < nseg; ++seg) {
+                    constexpr int CPR = HD / 8;                                    // 16-byte chunks per row
+                    constexpr int NCHUNK = C::RPB * CPR;
+                    constexpr int ITEMS = (NCHUNK + C::NCW * 32 - 1) / (C::NCW * 32);   // chunks per thread
+                    const int sf = seg ? f2 : f, su = seg ? u2 : cur_u;
+                    const int srb = su / a.Hkv, shkv = su % a.Hkv;
+                    unsigned char* dst = seg ? qtile2 : qtile;
+                    const bool chunked = a.cos == nullptr || chunked_rope_ok(a.cos, a.sin, a.R, HD);
+                    const int ctid = tid - 32;
+                    uint4 val[ITEMS];
+                    bool live[ITEMS];
 #pragma unroll
-                for (int k = 0; k < ITEMS; ++k) {
-                    const int item = ctid + k * (C::NCW * 32);
-                    const int r = item / CPR, ch = item % CPR;
-                    if (item < NCHUNK)
-                        *reinterpret_cast<uint4*>(qtile + r * C::QPITCH + ch * 16) = live[k] ? val[k] : make_uint4(0u, 0u, 0u, 0u);
+                    for (int k = 0; k < ITEMS; ++k) {          // all loads of all chunks are issued before any is used
+                        const int item = ctid + k * (C::NCW * 32);
+                        const int r = item / CPR, ch = item % CPR;
+                        const int gr = srb * C::RPB + r;
+                        live[k] = item < NCHUNK && gr < a.rows_total;
+                        const RowId id = decode_row(live[k] ? gr : 0, a.G, a.S);
+                        const int hq = shkv * a.G + id.g;
+                        if (a.cos == nullptr) {
+                            val[k] = *reinterpret_cast<const uint4*>(
+                                q + ((size_t)((sf * a.W + id.w) * a.Hq + hq) * a.S + id.s) * HD + ch * 8);
+                        } else {
+                            const T* qrow = q + ((size_t)(id.w * a.Hq + hq) * a.S + id.s) * HD;
+                            const size_t tab = ((size_t)(sf * a.W + id.w) * a.S + id.s) * a.R;
+                            if (chunked) {
+                                val[k] = rotate_chunk<T>(qrow, a.cos + tab, a.sin + tab, ch, a.R);
+                            } else {
+                                uint32_t* o32 = reinterpret_cast<uint32_t*>(&val[k]);
+#pragma unroll
+                                for (int c = 0; c < 4; ++c)
+                                    o32[c] = pack2<T>(rope_channel<T>(qrow, a.cos + tab, a.sin + tab, ch * 8 + 2 * c, a.R),
+                                                      rope_channel<T>(qrow, a.cos + tab, a.sin + tab, ch * 8 + 2 * c + 1, a.R));
+                            }
+                        }
+                    }
+                    if (seg && ctid < C::RPB) {                // visibility limits of the pre-staged segment
+                        const int gr = srb * C::RPB + ctid;
+                        const int v2 = vis[sf];
+                        int lim = v2;
+                        if (gr < a.rows_total) {
+                            const RowId id = decode_row(gr, a.G, a.S);
+                            lim = min(a.loc[(sf * a.W + id.w) * a.S + id.s], v2 - 1) + 1;
+                        }
+                        reinterpret_cast<int*>(qtile2 + C::QBYTES)[ctid] = lim;
+                    }
+#pragma unroll
+                    for (int k = 0; k < ITEMS; ++k) {
+                        const int item = ctid + k * (C::NCW * 32);
+                        const int r = item / CPR, ch = item % CPR;
+                        if (item < NCHUNK)
+                            *reinterpret_cast<uint4*>(dst + r * C::QPITCH + ch * 16) = live[k] ? val[k] : make_uint4(0u, 0u, 0u, 0u);
+                    }
                 }
+                if (warp == 1) HOGATT_TL(1, 21);
+                if (!consumer_sync()) break;                   // the query tile is complete
+                if (warp == 1) HOGATT_TL(1, 22);
+                lim_a = valid_a ? min(loc_a, vf - 1) + 1 : vf;
+                lim_b = valid_b ? min(loc_b, vf - 1) + 1 : vf;
             }
-            if (warp == 1) HOGATT_TL(1, 21);
-            if (!consumer_sync()) break;                       // the query tile is complete
-            if (warp == 1) HOGATT_TL(1, 22);
             {
-                const uint32_t qaddr = smem_u32(qtile) + (mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * C::QPITCH + (lane >> 4) * 16;
+                const uint32_t qaddr = smem_u32(qsrc) + (mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * C::QPITCH + (lane >> 4) * 16;
 #pragma unroll
                 for (int kk = 0; kk < C::KSTEPS; ++kk)
                     ldmatrix_x4(qaddr + kk * 32, qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3]);
             }
-            lim_a = valid_a ? min(loc_a, vf - 1) + 1 : vf;
-            lim_b = valid_b ? min(loc_b, vf - 1) + 1 : vf;
             if (want_rq && it == 0)
                 write_rotated_queries<T>(a.q, a.rq, a.cos, a.sin, a.F, a.W, a.Hq, a.S, HD, a.R,
                                          blockIdx.x * (C::NCW * 32) + tid - 32, gridDim.x * (C::NCW * 32));

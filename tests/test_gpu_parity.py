@@ -89,8 +89,8 @@ def test_launch_shape_matches_what_runs():
     assert 2 <= shape["cluster"] <= 16 and shape["ctas"] == 8 * shape["cluster"] <= sms
     # left to itself the library takes the persistent grid for this shape (67 MB of K/V) ...
     assert _cabi.launch_shape(mk(_cabi.KERNEL_AUTO))["kernels_per_call"] == 2
-    # ... and clusters for half the context
-    half = wl.baseline_problem("target", lengths=[4096] + [1024] * 4).to("cuda:0")
+    # ... and clusters for a quarter of the context
+    half = wl.baseline_problem("target", lengths=[2048] + [512] * 4).to("cuda:0")
     bp = _cabi.bind(out=out, queries=half.queries, locations=half.locations, keys=half.keys, values=half.values,
                     scale=half.scale, cos=half.cos, sin=half.sin)
     assert _cabi.launch_shape(bp)["kernel"] == _cabi.KERNEL_MMA_CLUSTER
