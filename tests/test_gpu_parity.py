@@ -164,6 +164,19 @@ def test_random_shapes_against_oracle(seed):
         check_against(r.out, ref.numpy(), p.dtype, what=f"seed {seed} kernel {k}")
 
 
+@pytest.mark.parametrize("kernel", [_cabi.KERNEL_AUTO, _cabi.KERNEL_MMA, _cabi.KERNEL_MMA_CLUSTER])
+def test_one_kv_head_spread_over_the_whole_gpu(kernel):
+    """What one rank sees when 8 kv heads are sharded over 8 GPUs: a single (kv head, row block) unit, cut into
+    one partial per SM on the persistent grid (the merge kernel's batched and strided passes both run) or into
+    one cluster of 16 CTAs."""
+    p = wl.make_problem("one_head", W=4, Hq=4, Hkv=1, E=128, S=1, lengths=[30000, 2048, 2048, 2048, 2049], theta=5e5,
+                        dtype=torch.bfloat16, seed=77)
+    ref, _ = oracle.fused(p.queries, p.cos, p.sin, p.locations, p.keys, p.values, p.scale)
+    r = run_cabi(p, kernel=kernel, want_rq=True)
+    assert r.rc == 0 and r.status == 0
+    check_against(r.out, ref.numpy(), p.dtype, what=f"one kv head, kernel {kernel}")
+
+
 def test_device_lengths_shorter_than_the_tensors():
     """fragment_lengths (device) may be shorter than the tensors' row extent: only that prefix is visible."""
     p = wl.edge_problem("ragged_bf16")
