@@ -108,6 +108,8 @@ def layer_problems(name: str, layers: int, rank: int, world: int, device):
         base = wl.baseline_problem(name, lengths=lengths)
     if world > 1:
         base = base.shard(rank, world)
+    elif EMULATE_SHARD > 1:       # what rank 0 of an N-way kv-head split computes, alone on this GPU (no gather)
+        base = base.shard(0, EMULATE_SHARD)
     d0 = base.to(device)
     probs = [d0]
     for i in range(1, layers):
@@ -119,6 +121,7 @@ def layer_problems(name: str, layers: int, rank: int, world: int, device):
 
 KERNEL_CHOICE = 0          # hogatt_kernel_choice passed to every call (--kernel)
 LENGTH_SCALE = 1.0         # --scale-lengths
+EMULATE_SHARD = 1          # --emulate-shard
 
 
 class CabiCall:
@@ -472,13 +475,16 @@ def main():
                     help="launch shape of the tensor-core kernel (auto = the library's own choice)")
     ap.add_argument("--scale-lengths", type=float, default=1.0,
                     help="multiply every fragment length of the workload (context-length sweeps; not the headline number)")
+    ap.add_argument("--emulate-shard", type=int, default=1,
+                    help="single GPU only: run rank 0's share of an N-way kv-head split (kernel tuning; not the headline number)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-rq", action="store_true", help="do not ask for the rotated-query side output")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     ap.add_argument("--no-isolated", action="store_true", help="skip the isolated cold-call leg (profiling runs)")
     args = ap.parse_args()
-    global KERNEL_CHOICE, LENGTH_SCALE
+    global KERNEL_CHOICE, LENGTH_SCALE, EMULATE_SHARD
     LENGTH_SCALE = args.scale_lengths
+    EMULATE_SHARD = args.emulate_shard
     KERNEL_CHOICE = {"auto": 0, "persistent": 2, "cluster": 3}[args.kernel]
     if args.workload == "cfg4":
         args.layers = min(args.layers, 4)          # 570 MB of KV per layer

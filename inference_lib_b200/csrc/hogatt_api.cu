@@ -276,11 +276,12 @@ int mma_best_cluster_dims(int HD, int MT, int dev, int F, int smem_optin, int un
 // and the second launch, but it only uses units * cluster SMs and one SM pulls about 66 GB/s: it wins
 // where the fixed costs dominate.  Fitted to measurements on B200 at 8 kv heads (us per call, B bytes
 // streamed, n CTAs; beyond 64 CTAs -- clusters of 10 -- the cluster shape did not get faster):
-//   persistent grid ~ 10.0 + 0.045 * partials per unit + B / 6.07 TB/s     (10.8 at 8 kv heads: 18.5 CTAs each)
+//   persistent grid ~ 8.5 + 0.12 * partials per unit + B / 6.07 TB/s     (10.7 at 8 kv heads: 18.5 CTAs each)
 //   cluster         ~ 8.5 + B / (min(n, 64) * 66 GB/s)
-// i.e. the cluster shape below about 32 MB per call at 8 kv heads, the persistent grid above; with fewer kv
-// heads per GPU (sharded) the persistent grid has more partials per head to merge and the crossover moves up.
-constexpr double kPersistFixedUs = 10.0, kPersistPerPartUs = 0.045, kClusterFixedUs = 8.5, kChipBytesPerUs = 6.07e6,
+// i.e. the cluster shape below about 30 MB per call at 8 kv heads, the persistent grid above; with fewer kv
+// heads per GPU (sharded 2, 4, 8 ways: 37, 74, 148 partials per head to merge) the crossover moves up -- the
+// north-star shape takes clusters on every rank from 2 GPUs on (17.3 / 17.0 / 16.8 us against 19.5 / 22.3 / 26.3).
+constexpr double kPersistFixedUs = 8.5, kPersistPerPartUs = 0.12, kClusterFixedUs = 8.5, kChipBytesPerUs = 6.07e6,
                  kSmBytesPerUs = 66e3;
 constexpr int kClusterUsefulCtas = 64;
 int choose_cluster(const hogatt_problem* p, const Resolved& r, int dev, int sms, int smem_optin, int64_t tiles_per_unit) {

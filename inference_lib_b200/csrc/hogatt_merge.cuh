@@ -12,19 +12,29 @@ constexpr int kMergeWarps = 4;
 // Partial p of the row lives at ws_o[(slot0 + p) * rpb + row][:], ws_m / ws_l likewise.
 // Same role as hogwild_attention_reduce_kernel (src/kernels/kernel_v21.cuh:605-656); that one
 // folds normalised partials pairwise by their log-sum-exp, here the partials are unnormalised.
-// Every load of the first kBatch partials -- their statistics (one partial per lane) and the lane's
-// four output columns of each -- is issued before any of them is used, so a row costs one memory
-// round trip; partials beyond kBatch (few units on many SMs) are folded in by a strided second pass.
-template <class T>
-__device__ __forceinline__ void merge_partials_row(const float* __restrict__ ws_o, const float* __restrict__ ws_m,
+// The statistics of all partials (lane-strided) and the lane's four output columns of the first kBatch
+// partials are all loaded before any is used: one memory round trip at 8 kv heads per GPU (19-20 partials
+// per row); every further batch of kBatch partials (fewer kv heads, more partials each) is one more.
+template <class T, int kMaxStat>
+__device__ __forceinline__ void merge_partials_rows(const float* __restrict__ ws_o, const float* __restrict__ ws_m,
                                                    const float* __restrict__ ws_l, size_t slot0, int rpb, int Ev,
                                                    int row, int count, T* const* bases, int nbases, size_t offset,
                                                    int lane) {
     constexpr int kBatch = 24;
-    const bool have = lane < count;
-    const float mp = have ? __ldcg(ws_m + (slot0 + lane) * rpb + row) : -INFINITY;
-    const float lp = have ? __ldcg(ws_l + (slot0 + lane) * rpb + row) : 0.f;
+    // kMaxStat: statistics held per lane (32 * kMaxStat partials per row without extra loads)
     const size_t pstride = (size_t)rpb * Ev;
+    // Issue everything the first batch needs before anything is used: the statistics of all partials
+    // (lane-strided) and the lane's four output columns of the first kBatch partials.
+    float mp[kMaxStat], lp[kMaxStat];
+#pragma unroll
+    for (int k = 0; k < kMaxStat; ++k) {
+        const int p = lane + 32 * k;
+        const bool have = p < count;
+        mp[k] = have ? __ldcg(ws_m + (slot0 + p) * rpb + row) : -INFINITY;
+        lp[k] = have ? __ldcg(ws_l + (slot0 + p) * rpb + row) : 0.f;
+    }
+    float M = -INFINITY, inv = 0.f;
+    bool blind = true;
     for (int e0 = 0; e0 < Ev; e0 += 128) {          // uniform trip count: the shuffles need every lane
         const int e = e0 + lane * 4;
         const bool mine = e < Ev;
@@ -33,37 +43,57 @@ __device__ __forceinline__ void merge_partials_row(const float* __restrict__ ws_
 #pragma unroll
         for (int k = 0; k < kBatch; ++k)
             x[k] = (k < count) ? __ldcg(reinterpret_cast<const float4*>(src + k * pstride)) : make_float4(0.f, 0.f, 0.f, 0.f);
-
-        float M = mp;
-        for (int p = lane + 32; p < count; p += 32) M = fmaxf(M, __ldcg(ws_m + (slot0 + p) * rpb + row));
+        if (e0 == 0) {
+            // weights 2^(m_p - M) (kept in mp[]) and the denominator
+            M = mp[0];
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
-        const float wp = (M == -INFINITY) ? 0.f : exp2f(mp - M);      // weight of partial `lane`
-        float den = wp * lp;
-        if (M != -INFINITY)
-            for (int p = lane + 32; p < count; p += 32)
-                den += __ldcg(ws_l + (slot0 + p) * rpb + row) * exp2f(__ldcg(ws_m + (slot0 + p) * rpb + row) - M);
+            for (int k = 1; k < kMaxStat; ++k) M = fmaxf(M, mp[k]);
+            for (int p = lane + 32 * kMaxStat; p < count; p += 32) M = fmaxf(M, __ldcg(ws_m + (slot0 + p) * rpb + row));
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
-        const bool blind = !(den > 0.f);
-        const float inv = blind ? 0.f : 1.f / den;
-
+            for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+            const bool dark = M == -INFINITY;
+            float den = 0.f;
+#pragma unroll
+            for (int k = 0; k < kMaxStat; ++k) {
+                mp[k] = dark ? 0.f : exp2f(mp[k] - M);
+                den = fmaf(lp[k], mp[k], den);
+            }
+            if (!dark)
+                for (int p = lane + 32 * kMaxStat; p < count; p += 32)
+                    den += __ldcg(ws_l + (slot0 + p) * rpb + row) * exp2f(__ldcg(ws_m + (slot0 + p) * rpb + row) - M);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
+            blind = !(den > 0.f);
+            inv = blind ? 0.f : 1.f / den;
+        }
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for (int k = 0; k < kBatch; ++k) {
-            const float wgt = __shfl_sync(0xffffffffu, wp, k);
+        for (int k = 0; k < kBatch; ++k) {          // kBatch <= 32: the weights of the first batch sit in mp[0]
+            const float wgt = __shfl_sync(0xffffffffu, mp[0], k);
             acc.x = fmaf(x[k].x, wgt, acc.x);
             acc.y = fmaf(x[k].y, wgt, acc.y);
             acc.z = fmaf(x[k].z, wgt, acc.z);
             acc.w = fmaf(x[k].w, wgt, acc.w);
         }
-        for (int p = kBatch; p < count; ++p) {
-            const float wgt = blind ? 0.f : exp2f(__ldcg(ws_m + (slot0 + p) * rpb + row) - M);
-            const float4 y = __ldcg(reinterpret_cast<const float4*>(src + p * pstride));
-            acc.x = fmaf(y.x, wgt, acc.x);
-            acc.y = fmaf(y.y, wgt, acc.y);
-            acc.z = fmaf(y.z, wgt, acc.z);
-            acc.w = fmaf(y.w, wgt, acc.w);
+        for (int p0 = kBatch; p0 < count; p0 += kBatch) {       // more partials: one round trip per further batch
+#pragma unroll
+            for (int k = 0; k < kBatch; ++k)
+                x[k] = (p0 + k < count) ? __ldcg(reinterpret_cast<const float4*>(src + (size_t)(p0 + k) * pstride))
+                                        : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int k = 0; k < kBatch; ++k) {
+                const int p = p0 + k;                           // warp-uniform
+                float wsel = mp[0];
+#pragma unroll
+                for (int q = 1; q < kMaxStat; ++q) wsel = ((p >> 5) == q) ? mp[q] : wsel;
+                float wgt = __shfl_sync(0xffffffffu, wsel, p & 31);
+                if (p >= 32 * kMaxStat)                         // beyond the per-lane table
+                    wgt = (blind || p >= count) ? 0.f : exp2f(__ldcg(ws_m + (slot0 + p) * rpb + row) - M);
+                acc.x = fmaf(x[k].x, wgt, acc.x);
+                acc.y = fmaf(x[k].y, wgt, acc.y);
+                acc.z = fmaf(x[k].z, wgt, acc.z);
+                acc.w = fmaf(x[k].w, wgt, acc.w);
+            }
         }
         if (blind) acc = make_float4(0.f, 0.f, 0.f, 0.f);
         if (mine) {
@@ -78,6 +108,20 @@ __device__ __forceinline__ void merge_partials_row(const float* __restrict__ ws_
             }
         }
     }
+}
+
+// Up to 32 partials per row (8 kv heads on 148 SMs: 19-20) take the lean instantiation; more (kv heads
+// sharded over GPUs: 37, 74, 148 per row) the one that keeps five statistics per lane.  Measured: the
+// general one alone costs +1.3 us at 19 partials, the lean one alone +4...6 us at 74-148.
+template <class T>
+__device__ __forceinline__ void merge_partials_row(const float* __restrict__ ws_o, const float* __restrict__ ws_m,
+                                                   const float* __restrict__ ws_l, size_t slot0, int rpb, int Ev,
+                                                   int row, int count, T* const* bases, int nbases, size_t offset,
+                                                   int lane) {
+    if (count <= 32)
+        merge_partials_rows<T, 1>(ws_o, ws_m, ws_l, slot0, rpb, Ev, row, count, bases, nbases, offset, lane);
+    else
+        merge_partials_rows<T, 5>(ws_o, ws_m, ws_l, slot0, rpb, Ev, row, count, bases, nbases, offset, lane);
 }
 
 // Split-K merge of the fragment op: grid (units, row groups), one warp per output row.
