@@ -391,7 +391,10 @@ int launch_all(const KernelArgs& args, const Resolved& r, int dev, int smem_opti
     if (getenv("HOGATT_SKIP_MERGE")) return HOGATT_OK;
 #endif
     dim3 mgrid((unsigned)r.units, (unsigned)ceil_div(r.rows_per_block, kMergeWarps));
-    HOGATT_CUDA_OK(launch_kernel(merge_kernel<T>, mgrid, dim3(kMergeWarps * 32), 0, stream, args));
+    if (args.parts_per_unit <= 32)
+        HOGATT_CUDA_OK(launch_kernel(merge_kernel<T, 1>, mgrid, dim3(kMergeWarps * 32), 0, stream, args));
+    else
+        HOGATT_CUDA_OK(launch_kernel(merge_kernel<T, 5>, mgrid, dim3(kMergeWarps * 32), 0, stream, args));
     return HOGATT_OK;
 }
 
@@ -400,7 +403,10 @@ int launch_all<float>(const KernelArgs& args, const Resolved& r, int dev, int sm
     int rc = launch_fma_dims<float>(args, dev, smem_optin, grid, stream);
     if (rc != HOGATT_OK) return rc;
     dim3 mgrid((unsigned)r.units, (unsigned)ceil_div(r.rows_per_block, kMergeWarps));
-    HOGATT_CUDA_OK(launch_kernel(merge_kernel<float>, mgrid, dim3(kMergeWarps * 32), 0, stream, args));
+    if (args.parts_per_unit <= 32)
+        HOGATT_CUDA_OK(launch_kernel(merge_kernel<float, 1>, mgrid, dim3(kMergeWarps * 32), 0, stream, args));
+    else
+        HOGATT_CUDA_OK(launch_kernel(merge_kernel<float, 5>, mgrid, dim3(kMergeWarps * 32), 0, stream, args));
     return HOGATT_OK;
 }
 

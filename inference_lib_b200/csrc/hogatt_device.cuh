@@ -171,9 +171,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // and every loop that sees a failed wait or the flag leaves without touching the tile.
 constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;
 
+// The polling loop lives out of line: these kernels run for microseconds and their instruction fetch
+// shows in the call time, so every wait site is just a try_wait and a call.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int bit);
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                                   int* status, int bit) {
     if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, abort_flag, status, bit);
+}
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int bit) {
     const uint64_t t0 = global_timer_ns();
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
@@ -376,7 +382,7 @@ __device__ __forceinline__ bool chunked_rope_ok(const float* c, const float* s, 
 // (`gthread` of `gthreads`).  Used when the caller wants the rotated queries back.  16-bit types
 // take the chunked path: one 16-byte chunk per thread per step, one memory round trip.
 template <class T>
-__device__ __forceinline__ void write_rotated_queries(const void* qv, void* rqv, const float* cos, const float* sin,
+__device__ __noinline__ void write_rotated_queries(const void* qv, void* rqv, const float* cos, const float* sin,
                                                       int F, int W, int Hq, int S, int E, int R, int gthread,
                                                       int gthreads) {
     T* __restrict__ rq = static_cast<T*>(rqv);
@@ -386,7 +392,7 @@ __device__ __forceinline__ void write_rotated_queries(const void* qv, void* rqv,
       if (chunked_rope_ok(cos, sin, R, E)) {
         const int cpr = E >> 3;
         const int items = rows * cpr;
-#pragma unroll 2
+#pragma unroll 1
         for (int item = gthread; item < items; item += gthreads) {
             const int row = item / cpr, ch = item - row * cpr;
             const int s = row % S;
@@ -403,7 +409,7 @@ __device__ __forceinline__ void write_rotated_queries(const void* qv, void* rqv,
       }
     }
     const int64_t items = (int64_t)rows * E;
-#pragma unroll 4
+#pragma unroll 1
     for (int64_t item = gthread; item < items; item += gthreads) {
         const int row = (int)(item / E), e = (int)(item - (int64_t)row * E);
         const int s = row % S;
@@ -426,10 +432,13 @@ __device__ __forceinline__ void write_rotated_queries(const void* qv, void* rqv,
 __device__ __forceinline__ void build_tile_prefix(const KernelArgs& a, int tile_tokens, int* vis, int* pre) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const int per = a.W * a.S;
+    // (loops kept rolled on purpose: this runs once per CTA and its instruction fetch is on the start-up path)
+#pragma unroll 1
     for (int f = warp; f < a.F; f += nwarps) {
         int top = -1;
         int cap = a.ft.e[f].rows;
         if (a.flen) cap = min(cap, a.flen[f]);            // issued together with the loads below
+#pragma unroll 1
         for (int i = lane; i < per; i += 32) top = max(top, a.loc[f * per + i]);
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) top = max(top, __shfl_xor_sync(0xffffffffu, top, o));
@@ -438,6 +447,7 @@ __device__ __forceinline__ void build_tile_prefix(const KernelArgs& a, int tile_
     __syncthreads();
     if (threadIdx.x == 0) {
         int acc = 0;
+#pragma unroll 1
         for (int f = 0; f < a.F; ++f) {
             pre[f] = acc;
             acc += ceil_div(vis[f], tile_tokens);

@@ -15,26 +15,30 @@ constexpr int kMergeWarps = 4;
 // The statistics of all partials (lane-strided) and the lane's four output columns of the first kBatch
 // partials are all loaded before any is used: one memory round trip at 8 kv heads per GPU (19-20 partials
 // per row); every further batch of kBatch partials (fewer kv heads, more partials each) is one more.
-template <class T, int kMaxStat>
+// `slots` partial slots exist for the row (an argument of the launch); how many of them hold a partial
+// (`count`) may itself come from memory: `count_of()` is evaluated only after the loads of the
+// statistics and of the first batch have been issued for ALL slots, so that the count's own load shares
+// their round trip; what an unused slot returned is discarded (selected away, never multiplied).
+template <class T, int kMaxStat, class CountFn>
 __device__ __forceinline__ void merge_partials_rows(const float* __restrict__ ws_o, const float* __restrict__ ws_m,
                                                    const float* __restrict__ ws_l, size_t slot0, int rpb, int Ev,
-                                                   int row, int count, T* const* bases, int nbases, size_t offset,
-                                                   int lane) {
+                                                   int row, int slots, CountFn count_of, T* const* bases, int nbases,
+                                                   size_t offset, int lane) {
     constexpr int kBatch = 24;
     // kMaxStat: statistics held per lane (32 * kMaxStat partials per row without extra loads)
     const size_t pstride = (size_t)rpb * Ev;
-    // Issue everything the first batch needs before anything is used: the statistics of all partials
-    // (lane-strided) and the lane's four output columns of the first kBatch partials.
     float mp[kMaxStat], lp[kMaxStat];
 #pragma unroll
     for (int k = 0; k < kMaxStat; ++k) {
         const int p = lane + 32 * k;
-        const bool have = p < count;
+        const bool have = p < slots;
         mp[k] = have ? __ldcg(ws_m + (slot0 + p) * rpb + row) : -INFINITY;
         lp[k] = have ? __ldcg(ws_l + (slot0 + p) * rpb + row) : 0.f;
     }
+    int count = 0;
     float M = -INFINITY, inv = 0.f;
     bool blind = true;
+#pragma unroll 1
     for (int e0 = 0; e0 < Ev; e0 += 128) {          // uniform trip count: the shuffles need every lane
         const int e = e0 + lane * 4;
         const bool mine = e < Ev;
@@ -42,13 +46,21 @@ __device__ __forceinline__ void merge_partials_rows(const float* __restrict__ ws
         float4 x[kBatch];
 #pragma unroll
         for (int k = 0; k < kBatch; ++k)
-            x[k] = (k < count) ? __ldcg(reinterpret_cast<const float4*>(src + k * pstride)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            x[k] = (k < slots) ? __ldcg(reinterpret_cast<const float4*>(src + k * pstride)) : make_float4(0.f, 0.f, 0.f, 0.f);
         if (e0 == 0) {
+            count = count_of();
+#pragma unroll
+            for (int k = 0; k < kMaxStat; ++k)
+                if (lane + 32 * k >= count) {
+                    mp[k] = -INFINITY;
+                    lp[k] = 0.f;
+                }
             // weights 2^(m_p - M) (kept in mp[]) and the denominator
             M = mp[0];
 #pragma unroll
             for (int k = 1; k < kMaxStat; ++k) M = fmaxf(M, mp[k]);
-            for (int p = lane + 32 * kMaxStat; p < count; p += 32) M = fmaxf(M, __ldcg(ws_m + (slot0 + p) * rpb + row));
+            if (kMaxStat > 1)
+                for (int p = lane + 32 * kMaxStat; p < count; p += 32) M = fmaxf(M, __ldcg(ws_m + (slot0 + p) * rpb + row));
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
             const bool dark = M == -INFINITY;
@@ -58,7 +70,7 @@ __device__ __forceinline__ void merge_partials_rows(const float* __restrict__ ws
                 mp[k] = dark ? 0.f : exp2f(mp[k] - M);
                 den = fmaf(lp[k], mp[k], den);
             }
-            if (!dark)
+            if (kMaxStat > 1 && !dark)
                 for (int p = lane + 32 * kMaxStat; p < count; p += 32)
                     den += __ldcg(ws_l + (slot0 + p) * rpb + row) * exp2f(__ldcg(ws_m + (slot0 + p) * rpb + row) - M);
 #pragma unroll
@@ -70,24 +82,30 @@ __device__ __forceinline__ void merge_partials_rows(const float* __restrict__ ws
 #pragma unroll
         for (int k = 0; k < kBatch; ++k) {          // kBatch <= 32: the weights of the first batch sit in mp[0]
             const float wgt = __shfl_sync(0xffffffffu, mp[0], k);
-            acc.x = fmaf(x[k].x, wgt, acc.x);
-            acc.y = fmaf(x[k].y, wgt, acc.y);
-            acc.z = fmaf(x[k].z, wgt, acc.z);
-            acc.w = fmaf(x[k].w, wgt, acc.w);
+            if (k < count) {                        // an unused slot may hold anything, NaN included
+                acc.x = fmaf(x[k].x, wgt, acc.x);
+                acc.y = fmaf(x[k].y, wgt, acc.y);
+                acc.z = fmaf(x[k].z, wgt, acc.z);
+                acc.w = fmaf(x[k].w, wgt, acc.w);
+            }
         }
-        for (int p0 = kBatch; p0 < count; p0 += kBatch) {       // more partials: one round trip per further batch
+        // more partials: one round trip per further batch.  The lean instantiation (at most 32 partials) only has
+        // 8 left; it is kept small on purpose -- this kernel runs for 2.5 us and its instruction fetch shows.
+        constexpr int kNext = (kMaxStat == 1) ? 32 - kBatch : kBatch;
+#pragma unroll 1
+        for (int p0 = kBatch; p0 < count; p0 += kNext) {
 #pragma unroll
-            for (int k = 0; k < kBatch; ++k)
+            for (int k = 0; k < kNext; ++k)
                 x[k] = (p0 + k < count) ? __ldcg(reinterpret_cast<const float4*>(src + (size_t)(p0 + k) * pstride))
                                         : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-            for (int k = 0; k < kBatch; ++k) {
+            for (int k = 0; k < kNext; ++k) {
                 const int p = p0 + k;                           // warp-uniform
                 float wsel = mp[0];
 #pragma unroll
                 for (int q = 1; q < kMaxStat; ++q) wsel = ((p >> 5) == q) ? mp[q] : wsel;
                 float wgt = __shfl_sync(0xffffffffu, wsel, p & 31);
-                if (p >= 32 * kMaxStat)                         // beyond the per-lane table
+                if (kMaxStat > 1 && p >= 32 * kMaxStat)         // beyond the per-lane table
                     wgt = (blind || p >= count) ? 0.f : exp2f(__ldcg(ws_m + (slot0 + p) * rpb + row) - M);
                 acc.x = fmaf(x[k].x, wgt, acc.x);
                 acc.y = fmaf(x[k].y, wgt, acc.y);
@@ -110,22 +128,12 @@ __device__ __forceinline__ void merge_partials_rows(const float* __restrict__ ws
     }
 }
 
-// Up to 32 partials per row (8 kv heads on 148 SMs: 19-20) take the lean instantiation; more (kv heads
-// sharded over GPUs: 37, 74, 148 per row) the one that keeps five statistics per lane.  Measured: the
-// general one alone costs +1.3 us at 19 partials, the lean one alone +4...6 us at 74-148.
-template <class T>
-__device__ __forceinline__ void merge_partials_row(const float* __restrict__ ws_o, const float* __restrict__ ws_m,
-                                                   const float* __restrict__ ws_l, size_t slot0, int rpb, int Ev,
-                                                   int row, int count, T* const* bases, int nbases, size_t offset,
-                                                   int lane) {
-    if (count <= 32)
-        merge_partials_rows<T, 1>(ws_o, ws_m, ws_l, slot0, rpb, Ev, row, count, bases, nbases, offset, lane);
-    else
-        merge_partials_rows<T, 5>(ws_o, ws_m, ws_l, slot0, rpb, Ev, row, count, bases, nbases, offset, lane);
-}
-
 // Split-K merge of the fragment op: grid (units, row groups), one warp per output row.
-template <class T>
+// NSTAT = 1 serves up to 32 partials per row (8 kv heads on 148 SMs: 19-20), NSTAT = 5 up to 160 without
+// extra loads (kv heads sharded over GPUs: 37, 74, 148 partials per row); the host picks by the number of
+// partial slots per unit.  Two kernels rather than one with both paths: the bigger code cost the common
+// case +1 us per call (instruction fetch of a kernel that runs for 2.5 us).
+template <class T, int NSTAT>
 __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const __grid_constant__ KernelArgs a) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int u = blockIdx.x;
@@ -133,23 +141,29 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const __grid_co
     HOGATT_SPAN_MIN(2);
     pdl_trigger();       // the next call's attention kernel may queue up behind this grid
     pdl_wait();          // partials are complete and visible once the attention grid has finished
-    const int TH = a.header[0], ctas = a.header[1];
     const int units = a.row_blocks * a.Hkv;
-    int first = 0, count = 0;
-    if (TH > 0) unit_ctas(u, TH, (int64_t)units * TH, ctas, &first, &count);
     const int RPB = a.rows_per_block, Ev = a.Ev;
+    // how many CTAs left a partial for this unit: from the header the attention kernel wrote
+    const int* hdr = a.header;
+    auto count_of = [=]() {
+        const int TH = __ldcg(hdr), ctas = __ldcg(hdr + 1);
+        int first = 0, count = 0;
+        if (TH > 0) unit_ctas(u, TH, (int64_t)units * TH, ctas, &first, &count);
+        return count;
+    };
     T* const local_out = static_cast<T*>(a.out);
     T* const* bases = a.world > 0 ? reinterpret_cast<T* const*>(a.peer_out) : &local_out;
     const int nbases = a.world > 0 ? a.world : 1;
     const int hq_all = a.world > 0 ? a.world * a.Hq : a.Hq;       // heads of the destination tensor
     const int hq_off = a.world > 0 ? a.rank * a.Hq : 0;           // where this rank's heads start in it
+#pragma unroll 1
     for (int row = blockIdx.y * kMergeWarps + warp; row < RPB; row += gridDim.y * kMergeWarps) {
         const int gr = rb * RPB + row;
         if (gr >= a.rows_total) continue;
         const RowId id = decode_row(gr, a.G, a.S);
         const size_t offset = ((size_t)(id.w * hq_all + hq_off + hkv * a.G + id.g) * a.S + id.s) * Ev;
-        merge_partials_row<T>(a.ws_o, a.ws_m, a.ws_l, (size_t)u * a.parts_per_unit, RPB, Ev, row, count, bases, nbases,
-                              offset, lane);
+        merge_partials_rows<T, NSTAT>(a.ws_o, a.ws_m, a.ws_l, (size_t)u * a.parts_per_unit, RPB, Ev, row, a.parts_per_unit,
+                                      count_of, bases, nbases, offset, lane);
     }
     HOGATT_SPAN_MAX(3);
 }

@@ -93,6 +93,18 @@ __host__ __device__ inline size_t mma_smem_bytes(int F) {
            ((size_t)2 * F + 1) * 4;
 }
 
+// rotate_chunk for tables or rotary sizes the 16-byte path cannot take (rotary_dim not a multiple of 16,
+// tables not 16-byte aligned): eight channels one by one.  Rare, and kept out of line.
+template <class T>
+__device__ __noinline__ uint4 rotate_chunk_by_channel(const T* q, const float* c, const float* s, int ch, int R) {
+    uint4 v;
+    uint32_t* o32 = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+        o32[k] = pack2<T>(rope_channel<T>(q, c, s, ch * 8 + 2 * k, R), rope_channel<T>(q, c, s, ch * 8 + 2 * k + 1, R));
+    return v;
+}
+
 // Destinations of a finished output row: this rank's `out`, or (fused all-gather) the full-size output of
 // every rank at this rank's head offset.
 template <class T>
@@ -205,6 +217,7 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
         int64_t u = CL ? (int64_t)(blockIdx.x / CS) : t0 / TH;
         int j = (int)(t0 - u * TH), fscan = 0, it = 0;
         bool ok = true;
+#pragma unroll 1
         for (int64_t t = t0; t < t1 && ok; ++t, ++it) {
             while (j >= pre[fscan + 1]) ++fscan;
             const int f = fscan;
@@ -283,6 +296,7 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
     int64_t u = CL ? (int64_t)(blockIdx.x / CS) : t0 / TH;
     int j = (int)(t0 - u * TH), fscan = 0, it = 0, cur_u = -1, cur_f = -1, hkv = 0, rb = 0;
     int pre_u = -1, pre_f = -1;          // the segment whose queries sit in the second tile
+#pragma unroll 1
     for (int64_t t = t0; t < t1; ++t, ++it) {
         if ((int)u != cur_u) {
             cur_u = (int)u;
@@ -367,15 +381,8 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
                         } else {
                             const T* qrow = q + ((size_t)(id.w * a.Hq + hq) * a.S + id.s) * HD;
                             const size_t tab = ((size_t)(sf * a.W + id.w) * a.S + id.s) * a.R;
-                            if (chunked) {
-                                val[k] = rotate_chunk<T>(qrow, a.cos + tab, a.sin + tab, ch, a.R);
-                            } else {
-                                uint32_t* o32 = reinterpret_cast<uint32_t*>(&val[k]);
-#pragma unroll
-                                for (int c = 0; c < 4; ++c)
-                                    o32[c] = pack2<T>(rope_channel<T>(qrow, a.cos + tab, a.sin + tab, ch * 8 + 2 * c, a.R),
-                                                      rope_channel<T>(qrow, a.cos + tab, a.sin + tab, ch * 8 + 2 * c + 1, a.R));
-                            }
+                            val[k] = chunked ? rotate_chunk<T>(qrow, a.cos + tab, a.sin + tab, ch, a.R)
+                                             : rotate_chunk_by_channel<T>(qrow, a.cos + tab, a.sin + tab, ch, a.R);
                         }
                     }
                     if (seg && ctid < C::RPB) {                // visibility limits of the pre-staged segment
@@ -443,6 +450,7 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
             // V rows past the end of a short tile were not written by the copy: make them finite
             // (their probabilities are exactly zero, but 0 * NaN would poison the sums).
             unsigned char* vgen = stages + (size_t)stage * C::STAGE_BYTES + C::KV_BYTES;
+#pragma unroll 1
             for (int r = 0; r < 8 * C::NT_S; ++r) {
                 const int g = r & 7, i = i0 + (r >> 3);
                 if (g * C::GT + i >= ntok && lane < C::ROWB / 16)

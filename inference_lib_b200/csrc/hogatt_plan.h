@@ -23,9 +23,22 @@
 
 namespace hogatt {
 
+// floor(num / den) for num >= 0, den > 0.  On the device a 64-bit division is a ~100-instruction routine; the
+// quotients here almost always fit 32 bits, so that case divides in 32 bits and the general one is kept out
+// of line (these run in kernels whose whole life is a few microseconds: code size and latency both show).
+#if defined(__CUDACC__)
+__host__ __device__ __noinline__ inline int64_t wide_div(int64_t num, int64_t den) { return num / den; }
+#else
+inline int64_t wide_div(int64_t num, int64_t den) { return num / den; }
+#endif
+HOGATT_HD int64_t floor_div(int64_t num, int64_t den) {
+    if ((((uint64_t)num | (uint64_t)den) >> 32) == 0) return (int64_t)((uint32_t)num / (uint32_t)den);
+    return wide_div(num, den);
+}
+
 // First global tile index of CTA c (c may equal ctas: end of the last range).
 HOGATT_HD int64_t cta_first_tile(int64_t c, int64_t total_tiles, int64_t ctas) {
-    return c * total_tiles / ctas;
+    return floor_div(c * total_tiles, ctas);
 }
 
 // CTAs that get work: never more than there are tiles, so every CTA owns at least one tile.
@@ -36,7 +49,7 @@ HOGATT_HD int effective_ctas(int64_t total_tiles, int grid) {
 // Smallest c whose range ends after tile x, i.e. the first CTA that touches tile x.
 HOGATT_HD int cta_of_tile(int64_t x, int64_t total_tiles, int64_t ctas) {
     // floor((c+1)*N/n) > x  <=>  (c+1)*N >= (x+1)*n  <=>  c >= ceil((x+1)*n/N) - 1
-    return (int)(((x + 1) * ctas + total_tiles - 1) / total_tiles - 1);
+    return (int)(floor_div((x + 1) * ctas + total_tiles - 1, total_tiles) - 1);
 }
 
 // First CTA touching unit u and how many consecutive CTAs touch it.

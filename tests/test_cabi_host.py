@@ -98,3 +98,16 @@ def test_ranges_tile_the_work_exactly_once(lib, th, units, grid):
         first, count = rng[2], rng[3]
         assert owners[u] == list(range(first, first + count)), "partial slots must match the CTAs that touch the unit"
         assert count <= parts_bound, "more partials than the workspace reserves"
+
+
+def test_cache_step_structs_match_the_header_and_refuse_bad_arguments(lib):
+    # hogatt_step_plan: 4 ints, 3 pointers, float + int, 3 pointers; hogatt_append: 8 ints, 2 x (pointer + 3 strides),
+    # 2 table pointers + 2 strides, 2 pointers, 2 ints, 3 host-array pointers, 3 pointers
+    assert C.sizeof(_cabi.StepPlan) == 16 + 24 + 8 + 24
+    assert C.sizeof(_cabi.Append) == 32 + 2 * (8 + 24) + 16 + 16 + 16 + 8 + 24 + 24
+    assert lib.hogatt_step_plan_launch(None, None) == -1
+    assert lib.hogatt_append_launch(None, None) == -1
+    sp = _cabi.StepPlan()
+    assert lib.hogatt_step_plan_launch(C.byref(sp), None) == -1          # no pointers at all
+    ap = _cabi.Append()
+    assert lib.hogatt_append_launch(C.byref(ap), None) == -1
