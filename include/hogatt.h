@@ -66,10 +66,10 @@ typedef enum hogatt_status {
  * launch shapes: a persistent grid (one CTA per SM over balanced tile ranges, partial results in the
  * workspace, a merge kernel after it) and a thread-block-cluster grid (one cluster per kv head and row
  * block, partial results merged through distributed shared memory inside the same kernel, nothing
- * written to the workspace).  AUTO takes the cluster shape for short contexts (below about 32 MB of K/V
- * per call at 8 kv heads on a B200; more when a GPU holds fewer kv heads), where the second launch and the workspace round trip dominate, and the
- * persistent grid otherwise; MMA forces the persistent grid, MMA_CLUSTER forces the cluster shape
- * (HOGATT_ERR_BAD_KERNEL_CHOICE when there are more units than half the SMs, or the device cannot
+ * written to the workspace).  AUTO takes the cluster shape when few units are left on the GPU (kv heads
+ * sharded over GPUs: each unit would leave 37-148 partials for the merge kernel) and the call is short
+ * enough for units x 16 SMs to stream it, and the persistent grid otherwise; MMA forces the persistent
+ * grid, MMA_CLUSTER forces the cluster shape (HOGATT_ERR_BAD_KERNEL_CHOICE when there are more units than half the SMs, or the device cannot
  * hold one cluster per unit at once).  hogatt_launch_shape() tells which one a problem gets. */
 typedef enum hogatt_kernel_choice {
     HOGATT_KERNEL_AUTO = 0,

@@ -273,17 +273,17 @@ int mma_best_cluster_dims(int HD, int MT, int dev, int F, int smem_optin, int un
 
 // CTAs per cluster if this problem runs as the self-merging cluster variant on the current device, else 0
 // (persistent grid + merge kernel).  The cluster variant saves the partials' trip through the workspace
-// and the second launch, but it only uses units * cluster SMs and one SM pulls about 66 GB/s: it wins
-// where the fixed costs dominate.  Fitted to measurements on B200 at 8 kv heads (us per call, B bytes
-// streamed, n CTAs; beyond 64 CTAs -- clusters of 10 -- the cluster shape did not get faster):
-//   persistent grid ~ 8.5 + 0.12 * partials per unit + B / 6.07 TB/s     (10.7 at 8 kv heads: 18.5 CTAs each)
-//   cluster         ~ 8.5 + B / (min(n, 64) * 66 GB/s)
-// i.e. the cluster shape below about 30 MB per call at 8 kv heads, the persistent grid above; with fewer kv
-// heads per GPU (sharded 2, 4, 8 ways: 37, 74, 148 partials per head to merge) the crossover moves up -- the
-// north-star shape takes clusters on every rank from 2 GPUs on (17.3 / 17.0 / 16.8 us against 19.5 / 22.3 / 26.3).
-constexpr double kPersistFixedUs = 8.5, kPersistPerPartUs = 0.12, kClusterFixedUs = 8.5, kChipBytesPerUs = 6.07e6,
+// and the second launch, but it only uses units * cluster SMs and one SM pulls about 66 GB/s.  Measured on
+// B200 (us per call, B bytes streamed, n CTAs, p = SMs / units partials per unit for the merge kernel):
+//   persistent grid ~ 8.9 + 0.12 * p + B / 6.5 TB/s        cluster ~ 9.0 + B / (min(n, 64) * 66 GB/s)
+// With 8 kv heads on the GPU (p = 18.5) the persistent grid wins at every context length (10.4 / 12.9 / 16.2 /
+// 20.6 us at 2K / 4K / 8K / 16K keys against 13.3 / 14.6 / 17.7 / 22.4); the cluster shape wins when the kv
+// heads are sharded over GPUs and few units are left per GPU, because then every unit has 37-148 partials to
+// merge: north-star shape at 2 / 4 / 8 GPUs 17.0 / 16.6 / 16.5 us against 18.6 / 20.6 / 23.4.
+constexpr double kPersistFixedUs = 8.9, kPersistPerPartUs = 0.12, kClusterFixedUs = 9.0, kChipBytesPerUs = 6.5e6,
                  kSmBytesPerUs = 66e3;
 constexpr int kClusterUsefulCtas = 64;
+constexpr int kClusterMinPartsPerUnit = 30;      // below that many partials per unit the merge kernel is cheap enough
 int choose_cluster(const hogatt_problem* p, const Resolved& r, int dev, int sms, int smem_optin, int64_t tiles_per_unit) {
     if (r.kernel != HOGATT_KERNEL_MMA || r.cluster_mode < 0 || 2 * r.units > sms) return 0;
     int cs = 0;
@@ -291,6 +291,7 @@ int choose_cluster(const hogatt_problem* p, const Resolved& r, int dev, int sms,
     if (p->dtype == HOGATT_BF16) cs = mma_best_cluster_dims<__nv_bfloat16>(p->E, r.mt, dev, p->F, smem_optin, r.units, sms);
     if (cs == 0 || r.cluster_mode > 0) return cs;
     if (p->max_ctas > 0) return 0;                       // the caller is testing grid sizes of the persistent variant
+    if (sms / r.units < kClusterMinPartsPerUnit) return 0;
     cs = std::min(cs, std::max(2, kClusterUsefulCtas / r.units));
     const double bytes = (double)tiles_per_unit * r.units * MmaCfg<128, 1>::STAGE_BYTES;
     const double persistent = kPersistFixedUs + kPersistPerPartUs * sms / r.units + bytes / kChipBytesPerUs;

@@ -382,9 +382,9 @@ __device__ __forceinline__ bool chunked_rope_ok(const float* c, const float* s, 
 // (`gthread` of `gthreads`).  Used when the caller wants the rotated queries back.  16-bit types
 // take the chunked path: one 16-byte chunk per thread per step, one memory round trip.
 template <class T>
-__device__ __noinline__ void write_rotated_queries(const void* qv, void* rqv, const float* cos, const float* sin,
-                                                      int F, int W, int Hq, int S, int E, int R, int gthread,
-                                                      int gthreads) {
+__device__ __noinline__ void write_rotated_queries(const void* qv, void* rqv, const float* __restrict__ cos,
+                                                   const float* __restrict__ sin, int F, int W, int Hq, int S, int E, int R,
+                                                   int gthread, int gthreads) {
     T* __restrict__ rq = static_cast<T*>(rqv);
     const T* __restrict__ q = static_cast<const T*>(qv);
     const int rows = F * W * Hq * S;
@@ -392,7 +392,9 @@ __device__ __noinline__ void write_rotated_queries(const void* qv, void* rqv, co
       if (chunked_rope_ok(cos, sin, R, E)) {
         const int cpr = E >> 3;
         const int items = rows * cpr;
-#pragma unroll 1
+        // four chunks per pass with all their loads in flight together (nothing here aliases): when one warp
+        // writes the whole share of its CTA in the middle of the K/V stream, a load takes 1.5-2 us
+#pragma unroll 4
         for (int item = gthread; item < items; item += gthreads) {
             const int row = item / cpr, ch = item - row * cpr;
             const int s = row % S;

@@ -19,14 +19,15 @@ constexpr int kMergeWarps = 4;
 // (`count`) may itself come from memory: `count_of()` is evaluated only after the loads of the
 // statistics and of the first batch have been issued for ALL slots, so that the count's own load shares
 // their round trip; what an unused slot returned is discarded (selected away, never multiplied).
+// One call handles 128 output columns (head sizes up to 128: the whole row); wider rows call it again.
 template <class T, int kMaxStat, class CountFn>
 __device__ __forceinline__ void merge_partials_rows(const float* __restrict__ ws_o, const float* __restrict__ ws_m,
                                                    const float* __restrict__ ws_l, size_t slot0, int rpb, int Ev,
                                                    int row, int slots, CountFn count_of, T* const* bases, int nbases,
-                                                   size_t offset, int lane) {
+                                                   size_t offset, int lane, int e0) {
     constexpr int kBatch = 24;
     // kMaxStat: statistics held per lane (32 * kMaxStat partials per row without extra loads)
-    const size_t pstride = (size_t)rpb * Ev;
+    const int pstride = rpb * Ev;                    // floats between consecutive partials of a row (32-bit offsets: less code)
     float mp[kMaxStat], lp[kMaxStat];
 #pragma unroll
     for (int k = 0; k < kMaxStat; ++k) {
@@ -38,16 +39,16 @@ __device__ __forceinline__ void merge_partials_rows(const float* __restrict__ ws
     int count = 0;
     float M = -INFINITY, inv = 0.f;
     bool blind = true;
-#pragma unroll 1
-    for (int e0 = 0; e0 < Ev; e0 += 128) {          // uniform trip count: the shuffles need every lane
+    {                                               // columns e0 .. e0 + 127 of the row; every lane takes part (shuffles)
         const int e = e0 + lane * 4;
         const bool mine = e < Ev;
         const float* src = ws_o + (slot0 * rpb + row) * Ev + (mine ? e : 0);
         float4 x[kBatch];
+        const int last_slot = slots - 1;             // slots past the last one re-read it (always a valid address)
 #pragma unroll
         for (int k = 0; k < kBatch; ++k)
-            x[k] = (k < slots) ? __ldcg(reinterpret_cast<const float4*>(src + k * pstride)) : make_float4(0.f, 0.f, 0.f, 0.f);
-        if (e0 == 0) {
+            x[k] = __ldcg(reinterpret_cast<const float4*>(src + min(k, last_slot) * pstride));
+        {
             count = count_of();
 #pragma unroll
             for (int k = 0; k < kMaxStat; ++k)
@@ -82,12 +83,11 @@ __device__ __forceinline__ void merge_partials_rows(const float* __restrict__ ws
 #pragma unroll
         for (int k = 0; k < kBatch; ++k) {          // kBatch <= 32: the weights of the first batch sit in mp[0]
             const float wgt = __shfl_sync(0xffffffffu, mp[0], k);
-            if (k < count) {                        // an unused slot may hold anything, NaN included
-                acc.x = fmaf(x[k].x, wgt, acc.x);
-                acc.y = fmaf(x[k].y, wgt, acc.y);
-                acc.z = fmaf(x[k].z, wgt, acc.z);
-                acc.w = fmaf(x[k].w, wgt, acc.w);
-            }
+            const bool used = k < count;            // an unused slot may hold anything, NaN included: select, do not multiply
+            acc.x = fmaf(used ? x[k].x : 0.f, wgt, acc.x);
+            acc.y = fmaf(used ? x[k].y : 0.f, wgt, acc.y);
+            acc.z = fmaf(used ? x[k].z : 0.f, wgt, acc.z);
+            acc.w = fmaf(used ? x[k].w : 0.f, wgt, acc.w);
         }
         // more partials: one round trip per further batch.  The lean instantiation (at most 32 partials) only has
         // 8 left; it is kept small on purpose -- this kernel runs for 2.5 us and its instruction fetch shows.
@@ -96,8 +96,7 @@ __device__ __forceinline__ void merge_partials_rows(const float* __restrict__ ws
         for (int p0 = kBatch; p0 < count; p0 += kNext) {
 #pragma unroll
             for (int k = 0; k < kNext; ++k)
-                x[k] = (p0 + k < count) ? __ldcg(reinterpret_cast<const float4*>(src + (size_t)(p0 + k) * pstride))
-                                        : make_float4(0.f, 0.f, 0.f, 0.f);
+                x[k] = __ldcg(reinterpret_cast<const float4*>(src + min(p0 + k, count - 1) * pstride));
 #pragma unroll
             for (int k = 0; k < kNext; ++k) {
                 const int p = p0 + k;                           // warp-uniform
@@ -162,8 +161,10 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const __grid_co
         if (gr >= a.rows_total) continue;
         const RowId id = decode_row(gr, a.G, a.S);
         const size_t offset = ((size_t)(id.w * hq_all + hq_off + hkv * a.G + id.g) * a.S + id.s) * Ev;
-        merge_partials_rows<T, NSTAT>(a.ws_o, a.ws_m, a.ws_l, (size_t)u * a.parts_per_unit, RPB, Ev, row, a.parts_per_unit,
-                                      count_of, bases, nbases, offset, lane);
+#pragma unroll 1
+        for (int e0 = 0; e0 < Ev; e0 += 128)
+            merge_partials_rows<T, NSTAT>(a.ws_o, a.ws_m, a.ws_l, (size_t)u * a.parts_per_unit, RPB, Ev, row, a.parts_per_unit,
+                                          count_of, bases, nbases, offset, lane, e0);
     }
     HOGATT_SPAN_MAX(3);
 }

@@ -200,9 +200,11 @@ __global__ void __launch_bounds__(kMergeWarps * 32) paged_merge_kernel(const __g
         int s_abs, hq;
         if (!paged_row(a, u, row, &s_abs, &hq)) continue;
         const int splits = a.splits;
-        merge_partials_rows<T, 1>(a.ws_o, a.ws_m, a.ws_l, (size_t)blockIdx.x * a.splits, kFmaRows, a.Ev, row, splits,
-                                  [splits]() { return splits; }, &out, 1,
-                                  (size_t)(u.w * a.o_w + s_abs * a.o_s + hq * a.o_h), lane);
+#pragma unroll 1
+        for (int e0 = 0; e0 < a.Ev; e0 += 128)
+            merge_partials_rows<T, 1>(a.ws_o, a.ws_m, a.ws_l, (size_t)blockIdx.x * a.splits, kFmaRows, a.Ev, row, splits,
+                                      [splits]() { return splits; }, &out, 1,
+                                      (size_t)(u.w * a.o_w + s_abs * a.o_s + hq * a.o_h), lane, e0);
     }
 }
 

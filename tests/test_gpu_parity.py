@@ -89,11 +89,13 @@ def test_launch_shape_matches_what_runs():
     assert 2 <= shape["cluster"] <= 16 and shape["ctas"] == 8 * shape["cluster"] <= sms
     # left to itself the library takes the persistent grid for this shape (67 MB of K/V) ...
     assert _cabi.launch_shape(mk(_cabi.KERNEL_AUTO))["kernels_per_call"] == 2
-    # ... and clusters for a quarter of the context
-    half = wl.baseline_problem("target", lengths=[2048] + [512] * 4).to("cuda:0")
-    bp = _cabi.bind(out=out, queries=half.queries, locations=half.locations, keys=half.keys, values=half.values,
-                    scale=half.scale, cos=half.cos, sin=half.sin)
-    assert _cabi.launch_shape(bp)["kernel"] == _cabi.KERNEL_MMA_CLUSTER
+    # ... and clusters for one rank's share of the same shape when the kv heads are spread over 4 GPUs
+    part = p.shard(0, 4).to("cuda:0")
+    out4 = torch.empty((part.W, part.Hq, part.S, part.Ev), dtype=p.dtype, device="cuda:0")
+    bp = _cabi.bind(out=out4, queries=part.queries, locations=part.locations, keys=part.keys, values=part.values,
+                    scale=part.scale, cos=part.cos, sin=part.sin)
+    shape = _cabi.launch_shape(bp)
+    assert shape["kernel"] == _cabi.KERNEL_MMA_CLUSTER and shape["cluster"] == 16 and shape["ctas"] == 32
 
 
 def test_causal_chunk_config_matches_reference(golden):
