@@ -35,7 +35,9 @@ extern "C" {
 #endif
 
 #define HOGATT_ABI_VERSION 1
+#ifndef HOGATT_MAX_FRAGMENTS
 #define HOGATT_MAX_FRAGMENTS 128   /* fragment table travels by value in the kernel arguments */
+#endif
 #define HOGATT_MAX_PEERS 8         /* GPUs of one node that can share a gathered output */
 
 typedef struct CUstream_st* hogatt_stream_t;   /* == cudaStream_t */
