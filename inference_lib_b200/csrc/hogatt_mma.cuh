@@ -68,10 +68,9 @@ struct MmaCfg {
     // Second query tile (+ one visibility limit per row): a CTA whose tile range runs on into a second fragment
     // or unit stages that segment's rotated queries at kernel start too, while ordinary loads still take one
     // quick round trip -- in the middle of the stream they queue behind megabytes of bulk copies.  Where the
-    // Only for 16-row blocks: with 32 rows the extra state pushed the streaming loop into register spills
-    // (+0.3 us measured), with 64 rows the shared memory has no room for it; those stage every segment when
-    // it is reached.
-    static constexpr int Q2BYTES = (MT == 1) ? QBYTES + RPB * 4 : 0;
+    // For 16- and 32-row blocks; with 64 rows the shared memory has no room for it and every segment is staged
+    // when it is reached.  (32 rows: a 20-byte spill outside the streaming loop; measured -0.1 us at GQA 5.)
+    static constexpr int Q2BYTES = (MT <= 2) ? QBYTES + RPB * 4 : 0;
     // cluster variant: what a CTA leaves in its own shared memory for the cluster-wide merge
     static constexpr int OPITCH = HD + 8;                // floats per partial row (padding: conflict-free float2 stores)
     static constexpr int CL_PART_FLOATS = 16 * OPITCH;   // one warp's 16 rows
