@@ -370,7 +370,7 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
                         pre_f = f2;
                     }
                 }
-                if (!consumer_sync()) break;                   // everyone is done with the previous query tile
+                if (it != 0 && !consumer_sync()) break;        // everyone is done with the previous query tile (there is none at the start)
                 if (warp == 1) HOGATT_TL(1, 20);
 #pragma unroll 1
                 for (int seg = 0; seg < nseg; ++seg) {
