@@ -79,6 +79,7 @@ SCENARIOS = {
     "bf16_s4_masked": dict(W=2, Hkv=2, E=64, R=64, layers=1, prompt=50, own=[8, 3], S=4, steps=2, theta=5e5, dtype="bfloat16",
                            new_tokens=[[4, 2], [1, 4]]),
     "f16_partial_rotary": dict(W=2, Hkv=1, E=64, R=32, layers=1, prompt=20, own=[4, 4], S=2, steps=2, theta=1e4, dtype="float16"),
+    "bf16_e128_w4": dict(W=4, Hkv=2, E=128, R=128, layers=1, prompt=100, own=[40, 17, 33, 8], S=1, steps=2, theta=5e5, dtype="bfloat16"),
     "f32_s2": dict(W=2, Hkv=2, E=32, R=32, layers=1, prompt=11, own=[3, 6], S=2, steps=2, theta=1e4, dtype="float32"),
 }
 
