@@ -44,13 +44,30 @@ NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.0103
 FALLBACK_HBM_GBS = 6650.0
 
 
-def measured_peak():
+FALLBACK_BF16_TFLOPS_SUSTAINED = 1400.0
+
+
+def measured_peak(key="hbm_gbs", fallback=FALLBACK_HBM_GBS):
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     try:
         with open(path) as fh:
-            return float(json.load(fh)["hbm_gbs"]), "measured (MEASURED_PEAKS.json)"
+            return float(json.load(fh)[key]), "measured (MEASURED_PEAKS.json)"
     except Exception:
-        return FALLBACK_HBM_GBS, "fallback"
+        return fallback, "fallback"
+
+
+def job_config(args, meta, world, fused_gather=True, graph=True):
+    """What the job is, identical for both arms (the reference arm times the same workload on the host cores)."""
+    lengths = meta["lengths"]
+    sz = 4 if meta["dtype"] == "float32" else 2
+    kv_bytes = meta["Hkv"] * sum(lengths) * (meta["E"] + meta["Ev"]) * sz
+    return {"workload": args.workload, **{k: v for k, v in meta.items() if k not in ("seed",)},
+            "layers_per_step": args.layers, "kv_bytes_resident": int(kv_bytes * args.layers),
+            "l2": "inputs larger than L2 (one distinct KV set per layer); isolated call uses an L2 flush",
+            "parallelism": (f"kv-head shard x{world}, output all-gather " +
+                            ("fused into the merge step (peer stores)" if fused_gather else "by NCCL")) if world > 1
+                           else "single GPU",
+            "cuda_graph": graph}
 
 
 class ClockSampler:
@@ -122,6 +139,8 @@ def layer_problems(name: str, layers: int, rank: int, world: int, device):
 KERNEL_CHOICE = 0          # hogatt_kernel_choice passed to every call (--kernel)
 LENGTH_SCALE = 1.0         # --scale-lengths
 EMULATE_SHARD = 1          # --emulate-shard
+HOST_PLAN = True           # --plan: the host passes the fragment lengths it knows (the tensors' row counts)
+STABLE_FRAGMENTS = 1       # --stable: the shared prompt (fragment 0) is not written during a decode step
 
 
 class CabiCall:
@@ -134,7 +153,8 @@ class CabiCall:
         self.rq = torch.empty((p.F, p.W, p.Hq, p.S, p.E), dtype=p.dtype, device=device) if want_rq else None
         self.bp = _cabi.bind(out=self.out, queries=p.queries, locations=p.locations, keys=p.keys, values=p.values,
                              scale=p.scale, fragment_lengths=p.fragment_lengths, cos=p.cos, sin=p.sin, rq=self.rq,
-                             kernel=KERNEL_CHOICE)
+                             kernel=KERNEL_CHOICE, host_lengths="rows" if HOST_PLAN else None,
+                             stable_fragments=STABLE_FRAGMENTS)
         # 1 when the attention kernel merges its split-K partials itself, 2 when merge_kernel follows
         self.kernels_per_call = _cabi.launch_shape(self.bp)["kernels_per_call"]
         need = _cabi.workspace_bytes(self.bp)
@@ -306,14 +326,32 @@ def run_ours(args):
     full, iso_us, clocks, graph_used, fused_gather = m["full"], m["iso_us"], m["clocks"], m["graph"], m["fused_gather"]
     launches_per_step = m["launches_per_step"]
     extra = None
-    if args.workload != "cfg4" and not args.no_extra:
-        # the long-context shape (139,264 keys, 570 MB of KV per call) beside the headline shape: the one whose
-        # per-GPU work stays far above the fixed per-call cost when the kv heads are spread over 8 GPUs
-        x = measure("cfg4", 4, 30, 5, False)
-        extra = {"cfg4": {"us_per_call": round(x["secs"] / x["n_calls"] * 1e6, 3),
-                          "value_TBps": round(x["bytes_per_call"] * x["n_calls"] / x["secs"] / 1e12, 4),
-                          "attention_only_us_per_call": round(x["secs_attn"] / x["n_calls"] * 1e6, 3) if x["secs_attn"] else None,
-                          "layers_per_step": x["layers"], "steps": 30, "bytes_per_call": x["bytes_per_call"]}}
+    if not args.no_extra:
+        # every other named shape beside the headline one, each with its own roofline fraction: the HBM-bound ones
+        # against the measured copy bandwidth, the dense chunked one (cfg5: its four groups are the four calls of a
+        # step) against the measured sustained bf16 tensor throughput
+        hbm_peak, _ = measured_peak()
+        tf_peak, _ = measured_peak("bf16_tflops_sustained", FALLBACK_BF16_TFLOPS_SUSTAINED)
+        extra = {}
+        for name, layers, steps, warm in (("cfg2", 32, 100, 10), ("cfg3", 32, 100, 10), ("target", 32, 100, 10),
+                                          ("cfg4", 4, 30, 5), ("cfg5", 4, 10, 3)):
+            if name == args.workload or (world > 1 and wl.BASELINE_CONFIGS[name]["Hkv"] % world):
+                continue
+            x = measure(name, layers, steps, warm, False)
+            t_call = x["secs"] / x["n_calls"]
+            t_kernel = (x["secs_attn"] or x["secs"]) / x["n_calls"]
+            e = {"us_per_call": round(t_call * 1e6, 3),
+                 "value_TBps": round(x["bytes_per_call"] / t_call / 1e12, 4),
+                 "attention_only_us_per_call": round(x["secs_attn"] / x["n_calls"] * 1e6, 3) if x["secs_attn"] else None,
+                 "layers_per_step": x["layers"], "steps": steps, "bytes_per_call": x["bytes_per_call"]}
+            if name == "cfg5":
+                flops = wl.baseline_problem(name).flops()
+                e.update({"bound": "tensor", "flops_per_call": flops,
+                          "achieved_TFLOPs_per_gpu": round(flops / world / t_kernel / 1e12, 1),
+                          "frac": round(flops / world / t_kernel / 1e12 / tf_peak, 4), "peak_TFLOPs": tf_peak})
+            else:
+                e.update({"bound": "hbm", "frac": round(x["bytes_per_call"] / world / t_kernel / 1e9 / hbm_peak, 4)})
+            extra[name] = e
     us_per_call = secs / n_calls * 1e6
     value = bytes_per_call * n_calls / secs / 1e12
 
@@ -326,18 +364,17 @@ def run_ours(args):
     peak, peak_src = measured_peak()
     per_gpu_bytes = bytes_per_call / world
     achieved = per_gpu_bytes / ((secs_attn or secs) / n_calls) / 1e9
+    tensor_bound = args.workload == "cfg5"          # ~1,000 flop per K/V byte: bounded by the tensor pipe, not by HBM
+    if tensor_bound:
+        tf_peak, tf_src = measured_peak("bf16_tflops_sustained", FALLBACK_BF16_TFLOPS_SUSTAINED)
+        tf = wl.baseline_problem(args.workload).flops() / world / ((secs_attn or secs) / n_calls) / 1e12
     line = {
         "metric": METRIC, "value": round(value, 4), "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(secs / args.steps * 1e3, 5), "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": str(full.dtype).replace("torch.", "") + " in, fp32 accumulate",
         "data": "synthetic (seeded N(0,1) q/k/v, keys pre-rotated)",
-        "config": {"workload": args.workload, **{k: v for k, v in full.meta.items() if k not in ("seed",)},
-                   "layers_per_step": m["layers"], "kv_bytes_resident": m["kv_resident"],
-                   "l2": "inputs larger than L2 (one distinct KV set per layer); isolated call uses an L2 flush",
-                   "parallelism": (f"kv-head shard x{world}, output all-gather " +
-                                   ("fused into the merge step (peer stores)" if fused_gather else "by NCCL")) if world > 1
-                                  else "single GPU",
-                   "cuda_graph": graph_used},
+        "config": job_config(args, wl.baseline_problem(args.workload).meta if world > 1 else full.meta, world,
+                             fused_gather or world == 1, graph_used),
         "us_per_call": round(us_per_call, 3),
         "us_per_call_isolated_cold": round(iso_us, 3),
         "pct_of_nominal_8TBps": round(100 * value * 1e3 / (NOMINAL_HBM_GBS * world), 2),
@@ -350,6 +387,11 @@ def run_ours(args):
                      "kernel": "mma_attention_kernel (+ merge_kernel in the same interval)",
                      "bytes_per_launch": int(per_gpu_bytes)},
     }
+    if tensor_bound:
+        line["roofline"] = {"bound": "tensor", "achieved": round(tf, 1), "peak": tf_peak, "unit": "TFLOP/s",
+                            "frac": round(tf / tf_peak, 4), "traffic": None, "peak_source": tf_src + ", sustained bf16",
+                            "kernel": "dense_attention_kernel (+ rope_kernel and merge_kernel in the same interval)",
+                            "flops_per_launch": int(wl.baseline_problem(args.workload).flops() / world)}
     if extra:
         line["other_workloads"] = extra
     if secs_attn:
@@ -389,34 +431,71 @@ def measure_e2e(args, p: wl.Problem, device, dist, world):
         hout.copy_(res, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
-    for _ in range(3):
-        call()
-    torch.cuda.synchronize()
-    if dist:
-        dist.barrier()
-    n = 10
-    t0 = time.perf_counter()
-    for _ in range(n):
-        call()
-    dt = (time.perf_counter() - t0) / n
-    tt = torch.tensor([dt], dtype=torch.float64, device=device)
-    if dist:
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-    dt = float(tt[0])
+    def call_resident():
+        # what a decode step pays: the KV cache stays on the device, only the step's queries and metadata come in
+        for d, h in zip([dq, dcos, dsin, dloc, dlen], [hq, hcos, hsin, hloc, hlen]):
+            d.copy_(h, non_blocking=True)
+        A.hogwild_fused(dq, dloc, dk, dv, p.scale, dlen, dcos, dsin, rotated_queries=rq, out=out)
+        res = out
+        if dist:
+            from inference_lib_b200 import sharded
+            res = sharded.gather_heads(out, world, gather_buffer=gathered)
+        hout.copy_(res, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    def median_time(fn, n):
+        for _ in range(5):
+            fn()
+        torch.cuda.synchronize()
+        if dist:
+            dist.barrier()
+        ts = []
+        for _ in range(n):
+            t0 = time.perf_counter()
+            fn()
+            ts.append(time.perf_counter() - t0)
+        tt = torch.tensor([statistics.median(ts)], dtype=torch.float64, device=device)
+        if dist:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        return float(tt[0])
+
+    n = 60
+    dt = median_time(call, n)
+    dt_res = median_time(call_resident, n)
     whole_bytes = wl.baseline_problem(args.workload).algorithmic_bytes() if world > 1 else p.algorithmic_bytes()
+    h2d_small = sum(t.numel() * t.element_size() for t in [hq, hcos, hsin, hloc, hlen])
     return {"value": round(whole_bytes / dt / 1e12, 5), "unit": UNIT, "us_per_call": round(dt * 1e6, 1),
-            "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
-            "what": "pinned host -> device copy of q/cos/sin/loc/lengths and all KV fragments, hogwild_fused, output back to host"}
+            "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "calls": n, "statistic": "median",
+            "what": "pinned host -> device copy of q/cos/sin/loc/lengths and all KV fragments, hogwild_fused, output back to host",
+            "kv_resident": {"value": round(whole_bytes / dt_res / 1e12, 5), "us_per_call": round(dt_res * 1e6, 1),
+                            "h2d_bytes_per_step": int(h2d_small), "d2h_bytes_per_step": int(d2h),
+                            "what": "KV cache resident on the device; only q/cos/sin/loc/lengths are copied in, output back to host"}}
 
 
 # ------------------------------------------------------------------------------------------------
 # CPU legs (the only places that run the oracle)
 # ------------------------------------------------------------------------------------------------
-def cpu_baseline(workload: str, budget_s: float, reps_cap: int = 5):
-    from oracle import hogwild_oracle as oracle
+def reference_runner(p: wl.Problem):
+    """One call of the op on the host cores: the reference's own ``hogwild_sdpa_pt`` fed by its
+    ``apply_rotary_pos_emb`` (python/hogwild/attention.py:38-67, :84-90, i.e. the eager branch :320-323) when the
+    module was staged under ``oracle/_ref``, else the restatement in ``oracle/`` (``kind: "port"``)."""
     torch.set_num_threads(os.cpu_count() or 1)
+    from oracle import build_oracle
+    ref = build_oracle.load_reference_python()
+    if ref is not None:
+        def run():
+            tiled = torch.tile(torch.unsqueeze(p.queries, 0), (p.cos.size(0), 1, 1, 1, 1))
+            rq = ref.apply_rotary_pos_emb(tiled, p.cos, p.sin, unsqueeze_dim=2)
+            return ref.hogwild_sdpa_pt(rq, p.locations, p.keys, p.values, p.scale)
+        return run, "reference", "the reference's hogwild_sdpa_pt + apply_rotary_pos_emb (python/hogwild/attention.py)"
+    from oracle import hogwild_oracle as oracle
+    return (lambda: oracle.fused(p.queries, p.cos, p.sin, p.locations, p.keys, p.values, p.scale), "port",
+            "the reference's PyTorch algorithm restated in oracle/ (the reference module was not staged)")
+
+
+def cpu_baseline(workload: str, budget_s: float, reps_cap: int = 5):
     p = wl.baseline_problem(workload)
-    run = lambda: oracle.fused(p.queries, p.cos, p.sin, p.locations, p.keys, p.values, p.scale)
+    run, kind, what = reference_runner(p)
     t0 = time.perf_counter(); run(); first = time.perf_counter() - t0
     reps = max(1, min(reps_cap, int(budget_s / max(first, 1e-3)) - 1))
     ts = []
@@ -424,19 +503,18 @@ def cpu_baseline(workload: str, budget_s: float, reps_cap: int = 5):
         t0 = time.perf_counter(); run(); ts.append(time.perf_counter() - t0)
     dt = statistics.median(ts)
     return {"value": round(p.algorithmic_bytes() / dt / 1e12, 7), "unit": UNIT, "us_per_call": round(dt * 1e6, 1),
-            "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"{reps} full calls of the '{workload}' problem (one layer) after 1 warm-up, median"}
+            "cores": torch.get_num_threads(), "kind": kind,
+            "sample": f"{reps} full calls of the '{workload}' problem (one layer) after 1 warm-up, median; {what}"}
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", 0))
     if rank != 0:
         return
-    from oracle import hogwild_oracle as oracle
-    torch.set_num_threads(os.cpu_count() or 1)
+    world = int(os.environ.get("WORLD_SIZE", 1))
     p = wl.baseline_problem(args.workload)
-    run = lambda: oracle.fused(p.queries, p.cos, p.sin, p.locations, p.keys, p.values, p.scale)
-    steps, warmup = min(args.steps, 8), min(args.warmup, 2)      # each step is one call: a bounded sample
+    run, kind, what = reference_runner(p)
+    steps, warmup = args.steps, args.warmup       # a step here is ONE call on one layer's tensors: a bounded sample
     for _ in range(warmup):
         run()
     t0 = time.perf_counter()
@@ -446,14 +524,14 @@ def run_reference(args):
     value = p.algorithmic_bytes() / dt / 1e12
     line = {
         "impl": "reference", "metric": METRIC, "value": round(value, 7), "unit": UNIT,
-        "n_gpus": int(os.environ.get("WORLD_SIZE", 1)), "steps": steps, "warmup": warmup,
+        "n_gpus": world, "steps": steps, "warmup": warmup,
         "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": str(p.dtype).replace("torch.", "") + " in, fp32 accumulate", "data": "synthetic (seeded N(0,1) q/k/v, keys pre-rotated)",
-        "config": {"workload": args.workload, **{k: v for k, v in p.meta.items() if k != "seed"},
-                   "step": "one call of the op on one layer's tensors (bounded sample of the 32-layer step)"},
+        "config": job_config(args, p.meta, world),
         "us_per_call": round(dt * 1e6, 1),
-        "cpu_baseline": {"value": round(value, 7), "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
-                         "sample": f"{steps} calls of the '{args.workload}' problem, reference PyTorch algorithm restated in oracle/"},
+        "cpu_baseline": {"value": round(value, 7), "unit": UNIT, "cores": torch.get_num_threads(), "kind": kind,
+                         "sample": f"{steps} timed steps, each ONE call of the '{args.workload}' problem on one layer's tensors "
+                                   f"(a bounded sample of the {args.layers}-call step; value is per-call throughput); {what}"},
         "e2e": {"value": round(value, 7), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -477,12 +555,23 @@ def main():
                     help="multiply every fragment length of the workload (context-length sweeps; not the headline number)")
     ap.add_argument("--emulate-shard", type=int, default=1,
                     help="single GPU only: run rank 0's share of an N-way kv-head split (kernel tuning; not the headline number)")
+    ap.add_argument("--plan", default="host", choices=["host", "device"],
+                    help="host: the call carries the fragment lengths the host knows, tiles are cut from them; "
+                         "device: tiles are derived on the device from locations / fragment_lengths")
+    ap.add_argument("--stable", type=int, default=1,
+                    help="leading fragments marked as not written by earlier work of the stream (the shared prompt)")
+    ap.add_argument("--pdl", default=None, choices=["0", "1"],
+                    help="programmatic dependent launch between the kernels of consecutive calls (default: the library's)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-rq", action="store_true", help="do not ask for the rotated-query side output")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     ap.add_argument("--no-isolated", action="store_true", help="skip the isolated cold-call leg (profiling runs)")
     args = ap.parse_args()
-    global KERNEL_CHOICE, LENGTH_SCALE, EMULATE_SHARD
+    global KERNEL_CHOICE, LENGTH_SCALE, EMULATE_SHARD, HOST_PLAN, STABLE_FRAGMENTS
+    HOST_PLAN = args.plan == "host"
+    STABLE_FRAGMENTS = args.stable
+    if args.pdl is not None:
+        os.environ["HOGATT_PDL"] = args.pdl          # read by the library when it is first used
     LENGTH_SCALE = args.scale_lengths
     EMULATE_SHARD = args.emulate_shard
     KERNEL_CHOICE = {"auto": 0, "persistent": 2, "cluster": 3}[args.kernel]

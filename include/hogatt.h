@@ -34,7 +34,7 @@
 extern "C" {
 #endif
 
-#define HOGATT_ABI_VERSION 1
+#define HOGATT_ABI_VERSION 2
 #ifndef HOGATT_MAX_FRAGMENTS
 #define HOGATT_MAX_FRAGMENTS 128   /* fragment table travels by value in the kernel arguments */
 #endif
@@ -72,12 +72,21 @@ typedef enum hogatt_status {
  * sharded over GPUs: each unit would leave 37-148 partials for the merge kernel) and the call is short
  * enough for units x 16 SMs to stream it, and the persistent grid otherwise; MMA forces the persistent
  * grid, MMA_CLUSTER forces the cluster shape (HOGATT_ERR_BAD_KERNEL_CHOICE when there are more units than half the SMs, or the device cannot
- * hold one cluster per unit at once).  hogatt_launch_shape() tells which one a problem gets. */
+ * hold one cluster per unit at once).  hogatt_launch_shape() tells which one a problem gets.
+ *
+ * DENSE is the kernel for calls with many query rows per kv head (W x Hq/Hkv x S >= 128, e.g. workers that
+ * each issue a 16-token chunk), where the op is bound by the tensor pipe, not by HBM: 128-row query blocks,
+ * tcgen05.mma with accumulators in tensor memory, K / V / Q tiles fetched by tensor-map TMA.  f16 / bf16,
+ * E == Ev == 128, at most 16 fragments, and Hq/Hkv x S must divide 128 or be a multiple of it; AUTO takes it
+ * whenever a problem qualifies, DENSE forces it (HOGATT_ERR_BAD_KERNEL_CHOICE otherwise).  It reads rotated
+ * queries from memory, so the fused entry point first runs the stand-alone rotation kernel into `rq` (or into
+ * the workspace when rq is NULL): three kernels per call. */
 typedef enum hogatt_kernel_choice {
     HOGATT_KERNEL_AUTO = 0,
     HOGATT_KERNEL_FMA = 1,
     HOGATT_KERNEL_MMA = 2,
-    HOGATT_KERNEL_MMA_CLUSTER = 3
+    HOGATT_KERNEL_MMA_CLUSTER = 3,
+    HOGATT_KERNEL_DENSE = 4
 } hogatt_kernel_choice;
 
 /*
@@ -118,6 +127,33 @@ typedef struct hogatt_problem {
                                  wait inside a kernel gives up (never expected in normal operation) */
     int32_t kernel;           /* hogatt_kernel_choice */
     int32_t max_ctas;         /* 0 = one CTA per SM; otherwise caps the persistent grid (testing)   */
+
+    /* Optional knowledge the host has about this call; both may stay 0 / NULL.
+     *
+     * host_lengths (host array of F ints, or NULL): for every fragment an UPPER BOUND, known on the
+     *   host, of the number of leading rows any query can see (the reference's callers hold exactly
+     *   this number: their fragment tensors end at the fragment's length, python/hogwild/attention.py:
+     *   26-35).  Values are clamped to [0, fragment_rows[f]].  When given, the tensor-core kernel cuts
+     *   the call into tiles from these numbers alone, so a CTA starts streaming keys and values
+     *   without first reading `locations` / `fragment_lengths` from device memory; visibility itself
+     *   is still decided on the device, row by row, from `locations` and `fragment_lengths`, so rows
+     *   between the true length and the bound are fetched and masked (their contents never reach a
+     *   result, whatever they hold).  NULL: the tiles are derived on the device from `locations` and
+     *   `fragment_lengths` (exact; one dependent memory round trip at the start of every CTA).
+     *
+     * stable_fragments: the keys and values of fragments 0 .. stable_fragments-1 were complete before
+     *   the stream's last few kernels were enqueued and nothing enqueued since writes them (the shared
+     *   prompt of a decode step, as opposed to the workers' fragments that the step has just appended
+     *   to).  With host_lengths given and programmatic dependent launch in use (the default; the
+     *   environment variable HOGATT_PDL=0 turns it off), the
+     *   kernel fetches its first tiles of those fragments BEFORE it waits for the stream's preceding
+     *   kernel, i.e. while that kernel -- and, if that kernel itself was allowed to start early, the
+     *   one before it -- may still be running; after one of this library's calls that is that call's
+     *   own two kernels and nothing older.  Everything else -- queries, tables, locations, lengths,
+     *   the other fragments, every store -- is touched only after the wait.  0: nothing is read early. */
+    const int32_t* host_lengths;
+    int32_t stable_fragments;
+    int32_t reserved_;
 } hogatt_problem;
 
 /* ABI version compiled into the library (== HOGATT_ABI_VERSION of the header it was built from). */

@@ -14,7 +14,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG, "libhogatt_b200.so")
 
 F32, F16, BF16 = 0, 1, 2
-KERNEL_AUTO, KERNEL_FMA, KERNEL_MMA, KERNEL_MMA_CLUSTER = 0, 1, 2, 3
+KERNEL_AUTO, KERNEL_FMA, KERNEL_MMA, KERNEL_MMA_CLUSTER, KERNEL_DENSE = 0, 1, 2, 3, 4
 MAX_FRAGMENTS = 128
 
 EXPORTS = ["hogatt_abi_version", "hogatt_status_string", "hogatt_last_cuda_error", "hogatt_workspace_bytes",
@@ -33,6 +33,7 @@ class Problem(C.Structure):
         ("fragment_rows", C.POINTER(C.c_int32)),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("device_status", C.c_void_p),
         ("kernel", C.c_int32), ("max_ctas", C.c_int32),
+        ("host_lengths", C.POINTER(C.c_int32)), ("stable_fragments", C.c_int32), ("reserved_", C.c_int32),
     ]
 
 
@@ -152,11 +153,14 @@ class BoundProblem:
 
 
 def bind(*, out, queries, locations, keys, values, scale, fragment_lengths=None, cos=None, sin=None, rq=None,
-         workspace=None, status=None, kernel=KERNEL_AUTO, max_ctas=0) -> BoundProblem:
+         workspace=None, status=None, kernel=KERNEL_AUTO, max_ctas=0, host_lengths=None,
+         stable_fragments=0) -> BoundProblem:
     """Fill a ``Problem`` from torch CUDA tensors (pointers only; nothing is copied).
 
     ``queries`` is ``[W,Hq,S,E]`` with ``cos``/``sin`` given (fused entry point) or ``[F,W,Hq,S,E]``
-    already rotated.  Fragments may be ``[Hkv,L,E]`` or ``[1,Hkv,L,E]``.
+    already rotated.  Fragments may be ``[Hkv,L,E]`` or ``[1,Hkv,L,E]``.  ``host_lengths``: a list of
+    F ints (upper bounds of the visible lengths that the host knows) or ``"rows"`` for the tensors'
+    own row counts; ``stable_fragments``: leading fragments nothing enqueued earlier still writes.
     """
     F = len(keys)
     W, Hq, S, Ev = out.shape
@@ -177,9 +181,16 @@ def bind(*, out, queries, locations, keys, values, scale, fragment_lengths=None,
     p.value_fragments = C.cast(vp, C.POINTER(C.c_void_p))
     p.fragment_rows = C.cast(rows, C.POINTER(C.c_int32))
     p.device_status = status.data_ptr() if status is not None else None
+    hl = None
+    if host_lengths is not None:
+        vals = [int(k.shape[-2]) for k in keys] if isinstance(host_lengths, str) else [int(x) for x in host_lengths]
+        assert len(vals) == F
+        hl = (C.c_int32 * F)(*vals)
+        p.host_lengths = C.cast(hl, C.POINTER(C.c_int32))
+    p.stable_fragments = int(stable_fragments)
     if workspace is not None:
         p.workspace, p.workspace_bytes = workspace.data_ptr(), workspace.numel() * workspace.element_size()
-    return BoundProblem(p, [kp, vp, rows, out, queries, locations, keys, values, fragment_lengths, cos, sin, rq,
+    return BoundProblem(p, [hl, kp, vp, rows, out, queries, locations, keys, values, fragment_lengths, cos, sin, rq,
                             workspace, status])
 
 

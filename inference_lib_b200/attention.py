@@ -41,6 +41,22 @@ def hogwild_fused(queries: torch.Tensor, locations: torch.Tensor, keys: List[tor
     return out
 
 
+def hogwild_fused_planned(queries: torch.Tensor, locations: torch.Tensor, keys: List[torch.Tensor],
+                          values: List[torch.Tensor], scale: float, fragment_lengths: torch.Tensor, cosines: torch.Tensor,
+                          sines: torch.Tensor, *, rotated_queries: torch.Tensor, out: torch.Tensor,
+                          host_lengths: List[int], stable_fragments: int = 0) -> torch.Tensor:
+    """:func:`hogwild_fused` for fragments kept in preallocated slabs ``[Hkv, capacity, E]`` (no copies are made;
+    the slabs must be contiguous).  ``host_lengths[f]`` is an upper bound, known on the host, of fragment ``f``'s
+    current length (the true lengths stay on the device in ``fragment_lengths``); ``stable_fragments`` leading
+    fragments are not written by work enqueued before this call, e.g. the shared prompt.  With both, the kernel
+    starts streaming keys and values without reading anything from device memory first.  No counterpart in the
+    reference, whose fragment tensors always end at the fragment's length."""
+    torch.ops.libhogatt.hogwild_fused_planned(out, rotated_queries, scale, locations, queries.contiguous(),
+                                              fragment_lengths, keys, values, cosines, sines,
+                                              [int(x) for x in host_lengths], int(stable_fragments))
+    return out
+
+
 def hogwild_sdpa(queries: torch.Tensor, locations: torch.Tensor, keys: List[torch.Tensor], values: List[torch.Tensor],
                  scale: float, fragment_lengths: Optional[torch.Tensor] = None,
                  out: Optional[torch.Tensor] = None) -> torch.Tensor:

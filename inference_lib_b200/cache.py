@@ -34,6 +34,8 @@ class CacheStructure:
     cos: torch.Tensor             # [F,W,S,R] fp32: tables to rotate the queries with
     sin: torch.Tensor
     loc: torch.Tensor             # [F,W,S] int32
+    host_lengths: Optional[List[int]] = None   # per fragment: an upper bound of frags[f] that the host knows
+    stable: int = 0               # leading fragments that no worker appends to
 
 
 class FragmentCache:
@@ -54,6 +56,8 @@ class FragmentCache:
         # lengths[layer][flip]: the buffer index `cur[layer]` holds the valid lengths
         self.lengths = [[torch.zeros(self.F, dtype=torch.int32, device=self.device) for _ in range(2)] for _ in range(layers)]
         self.cur = [0] * layers
+        # what the host knows without reading anything back: an upper bound of every length (appends add at most S)
+        self.host_lengths = [[0] * self.F for _ in range(layers)]
         rows = [list(o) + [-1] * (self.F - len(o)) for o in order]
         self.order = torch.tensor(rows, dtype=torch.int32, device=self.device)
         self.write_to = [int(x) for x in (write_to if write_to is not None else [o[-1] for o in order])]
@@ -71,6 +75,7 @@ class FragmentCache:
             self.keys[layer][f][:, :L].copy_(keys[layer])
             self.values[layer][f][:, :L].copy_(values[layer])
             self.lengths[layer][self.cur[layer]][f] = L
+            self.host_lengths[layer][f] = int(L)
 
     def frags(self, layer: int = 0) -> torch.Tensor:
         return self.lengths[layer][self.cur[layer]]
@@ -91,6 +96,8 @@ class FragmentCache:
         if rc != 0:
             raise RuntimeError(f"hogatt_append_launch: {_cabi.status_string(rc)}")
         self.cur[layer] = 1 - self.cur[layer]
+        for f in self.write_to:
+            self.host_lengths[layer][f] = min(self.capacities[f], self.host_lengths[layer][f] + S)
         if layer == 0:
             R = 2 * self.inv_freq.numel()
             if self.loc is None or self.loc.shape[2] != S:
@@ -102,7 +109,8 @@ class FragmentCache:
                                  round_tables_to=self.round_to, stream=stream)
             if rc != 0:
                 raise RuntimeError(f"hogatt_step_plan_launch: {_cabi.status_string(rc)}")
-        return CacheStructure(keys=self.keys[layer], values=self.values[layer], frags=dst, cos=self.cos, sin=self.sin, loc=self.loc)
+        return CacheStructure(keys=self.keys[layer], values=self.values[layer], frags=dst, cos=self.cos, sin=self.sin,
+                              loc=self.loc, host_lengths=list(self.host_lengths[layer]), stable=min(self.write_to))
 
     # ---- merge_caches ----------------------------------------------------------------------------------------
     def merge(self, target: int, source: int):
@@ -127,3 +135,5 @@ class FragmentCache:
             if rc != 0:
                 raise RuntimeError(f"hogatt_append_launch: {_cabi.status_string(rc)}")
             self.cur[layer] = 1 - self.cur[layer]
+            self.host_lengths[layer][target] = min(self.capacities[target],
+                                                   self.host_lengths[layer][target] + self.host_lengths[layer][source])

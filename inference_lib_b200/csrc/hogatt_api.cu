@@ -12,6 +12,10 @@
 #include "hogatt_mma.cuh"
 #include "hogatt_paged.cuh"
 #include "hogatt_cache.cuh"
+#include "hogatt_dense.cuh"
+
+#include <mutex>
+#include <unordered_map>
 
 namespace hogatt {
 namespace {
@@ -65,14 +69,42 @@ int ensure_smem_limit(Kernel kernel, int dev, size_t bytes, std::atomic<size_t>*
 }
 
 // Launch with the programmatic-stream-serialization attribute: the kernel may be scheduled while its
-// stream predecessor is still running (each of our kernels calls griddepcontrol.wait before it
-// touches global memory).  Off unless HOGATT_PDL=1 is set in the environment when the library is first used.
+// stream predecessor is still running (each of our kernels calls griddepcontrol.wait before it touches
+// global memory that earlier work may write -- everything except the K/V rows of fragments the caller
+// declared stable).  On unless HOGATT_PDL=0 is set in the environment when the library is first used.
 bool pdl_enabled() {
     static const bool on = [] {
         const char* v = getenv("HOGATT_PDL");
-        return v && v[0] == '1';
+        return !(v && v[0] == '0');
     }();
     return on;
+}
+
+int tune_flags() {
+    static const int v = [] {
+        const char* e = getenv("HOGATT_TUNE");
+        return e ? atoi(e) : 0;
+    }();
+    return v;
+}
+
+// HOGATT_DENSE=0 in the environment keeps AUTO away from the tcgen05 kernel (A/B measurements).
+bool dense_disabled() {
+    static const bool off = [] {
+        const char* v = getenv("HOGATT_DENSE");
+        return v && v[0] == '0';
+    }();
+    return off;
+}
+
+// HOGATT_HOST_PLAN=0 in the environment (read when the library is first used) makes every call derive its
+// tiles on the device even when the caller gave host_lengths: for A/B measurements.
+bool host_plan_disabled() {
+    static const bool off = [] {
+        const char* v = getenv("HOGATT_HOST_PLAN");
+        return v && v[0] == '0';
+    }();
+    return off;
 }
 
 template <class... KArgs, class... Args>
@@ -113,6 +145,17 @@ bool mma_eligible(const hogatt_problem* p) {
     return true;
 }
 
+// The tcgen05 kernel: 16-bit types, head size 128, at least one full 128-row query block per kv head, and a block
+// must be a whole box of the rotated-query tensor [F, W, Hkv, G*S, E]: either whole workers (G*S divides 128) or a
+// slice of one worker's rows (128 divides G*S).  Tensor maps travel in the kernel arguments, hence the fragment cap.
+bool dense_eligible(const hogatt_problem* p) {
+    if (p->dtype != HOGATT_F16 && p->dtype != HOGATT_BF16) return false;
+    if (p->E != 128 || p->Ev != 128 || p->F > kDenseMaxFragments) return false;
+    const int64_t gs = (int64_t)(p->Hq / p->Hkv) * p->S;
+    if ((int64_t)p->W * gs < kDenseRows) return false;
+    return gs <= kDenseRows ? kDenseRows % gs == 0 : gs % kDenseRows == 0;
+}
+
 bool fma_eligible(const hogatt_problem* p) {
     const int vec = 16 / (int)dtype_size(p->dtype);
     if (p->Ev != 32 && p->Ev != 64 && p->Ev != 128 && p->Ev != 256) return false;
@@ -134,8 +177,16 @@ int resolve(const hogatt_problem* p, Resolved* r) {
     r->cluster = 0;
     r->cluster_forced = kernel == HOGATT_KERNEL_MMA_CLUSTER;
     if (kernel == HOGATT_KERNEL_MMA_CLUSTER) kernel = HOGATT_KERNEL_MMA;
-    if (kernel == HOGATT_KERNEL_AUTO) kernel = mma_eligible(p) ? HOGATT_KERNEL_MMA : HOGATT_KERNEL_FMA;
-    if (kernel == HOGATT_KERNEL_MMA) {
+    if (kernel == HOGATT_KERNEL_AUTO)
+        kernel = (dense_eligible(p) && !dense_disabled()) ? HOGATT_KERNEL_DENSE
+                                                           : (mma_eligible(p) ? HOGATT_KERNEL_MMA : HOGATT_KERNEL_FMA);
+    if (kernel == HOGATT_KERNEL_DENSE) {
+        if (!dense_eligible(p)) return HOGATT_ERR_BAD_KERNEL_CHOICE;
+        r->cluster_mode = -1;
+        r->mt = 0;
+        r->rows_per_block = kDenseRows;
+        r->tile_tokens = kDenseTile;
+    } else if (kernel == HOGATT_KERNEL_MMA) {
         if (!mma_eligible(p)) return HOGATT_ERR_BAD_KERNEL_CHOICE;
         r->mt = rows_total <= 16 ? 1 : (rows_total <= 32 ? 2 : 4);
         r->rows_per_block = 16 * r->mt;
@@ -157,7 +208,7 @@ int resolve(const hogatt_problem* p, Resolved* r) {
 }
 
 struct WorkspaceLayout {
-    size_t header, o, m, l, total;
+    size_t header, o, m, l, rq, total;
     int parts;
 };
 
@@ -169,7 +220,10 @@ WorkspaceLayout carve(const hogatt_problem* p, const Resolved& r, int grid) {
     w.o = 256;
     w.m = w.o + align_up(slots * p->Ev * sizeof(float), 256);
     w.l = w.m + align_up(slots * sizeof(float), 256);
-    w.total = w.l + align_up(slots * sizeof(float), 256);
+    w.rq = w.l + align_up(slots * sizeof(float), 256);
+    // the tcgen05 kernel reads rotated queries from memory: room for them in case the caller does not want them back
+    w.total = w.rq + (r.kernel == HOGATT_KERNEL_DENSE
+                          ? align_up((size_t)p->F * p->W * p->Hq * p->S * p->E * dtype_size(p->dtype), 256) : 0);
     return w;
 }
 
@@ -183,7 +237,11 @@ int cluster_upper_bound(const Resolved& r, int sms) {
 
 int64_t tiles_upper_bound(const hogatt_problem* p, const Resolved& r) {
     int64_t th = 0;
-    for (int f = 0; f < p->F; ++f) th += ceil_div(p->fragment_rows[f] < 0 ? 0 : p->fragment_rows[f], r.tile_tokens);
+    for (int f = 0; f < p->F; ++f) {
+        int rows = p->fragment_rows[f] < 0 ? 0 : p->fragment_rows[f];
+        if (p->host_lengths) rows = std::max(0, std::min(rows, p->host_lengths[f]));
+        th += ceil_div(rows, r.tile_tokens);
+    }
     return th;
 }
 
@@ -372,10 +430,116 @@ int launch_fma_dims(const KernelArgs& args, int dev, int smem_optin, int grid, c
     return HOGATT_ERR_UNSUPPORTED_HEAD_DIM;
 }
 
+// ---- tcgen05 kernel: tensor maps and launch ------------------------------------------------------------------
+// cuTensorMapEncodeTiled comes from the driver; it is looked up through the runtime so that the library links
+// against nothing but cudart.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn tensor_map_encoder() {
+    static EncodeTiledFn fn = [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess) {
+            (void)cudaGetLastError();
+            ptr = nullptr;
+        }
+        return reinterpret_cast<EncodeTiledFn>(ptr);
+    }();
+    return fn;
+}
+
+// A tiled map with the 128-byte swizzle over a dense row-major tensor of 16-bit elements: dims[0] is the contiguous
+// one, box[0] = 64 elements = 128 bytes.
+int encode_map(CUtensorMap* out, const void* base, int dtype, int rank, const cuuint64_t* dims, const cuuint32_t* box) {
+    EncodeTiledFn fn = tensor_map_encoder();
+    if (!fn) return HOGATT_ERR_CUDA;
+    cuuint64_t strides[4];
+    cuuint64_t acc = 2;
+    for (int i = 0; i + 1 < rank; ++i) {
+        acc *= dims[i];
+        strides[i] = acc;
+    }
+    const cuuint32_t ones[5] = {1, 1, 1, 1, 1};
+    const CUresult rc = fn(out, dtype == HOGATT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                           (cuuint32_t)rank, const_cast<void*>(base), dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (rc != CUDA_SUCCESS) {
+        tl_last_cuda_error = (int)rc;
+        return HOGATT_ERR_CUDA;
+    }
+    return HOGATT_OK;
+}
+
+// Fragment maps are cached by (pointer, rows, heads, dtype): preallocated slabs keep their pointers for the whole
+// generation, so a decode step encodes nothing.
+struct MapKey {
+    const void* ptr;
+    int rows, hkv, dtype;
+    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && hkv == o.hkv && dtype == o.dtype; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        return std::hash<const void*>()(k.ptr) ^ ((size_t)k.rows * 0x9E3779B97F4A7C15ull) ^ ((size_t)k.hkv << 48) ^ ((size_t)k.dtype << 56);
+    }
+};
+int fragment_map(const void* ptr, int rows, int Hkv, int dtype, CUtensorMap* out) {
+    static std::mutex mu;
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    const MapKey key{ptr, rows, Hkv, dtype};
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        auto it = cache.find(key);
+        if (it != cache.end()) {
+            *out = it->second;
+            return HOGATT_OK;
+        }
+    }
+    const cuuint64_t dims[3] = {128, (cuuint64_t)rows, (cuuint64_t)Hkv};
+    const cuuint32_t box[3] = {64, kDenseTile, 1};
+    const int rc = encode_map(out, ptr, dtype, 3, dims, box);
+    if (rc != HOGATT_OK) return rc;
+    std::lock_guard<std::mutex> lock(mu);
+    if (cache.size() >= 8192) cache.clear();
+    cache.emplace(key, *out);
+    return HOGATT_OK;
+}
+
 template <class T>
-int launch_all(const KernelArgs& args, const Resolved& r, int dev, int smem_optin, int grid, cudaStream_t stream) {
+int launch_dense(const KernelArgs& args, const void* q_rot, int dtype, int dev, int smem_optin, int grid, cudaStream_t stream) {
+    static std::atomic<size_t> granted[kMaxDevices];
+    const size_t smem = dense_smem_bytes(args.F);
+    if (smem > (size_t)smem_optin) return HOGATT_ERR_TOO_MANY_FRAGMENTS;
+    int rc = ensure_smem_limit(dense_attention_kernel<T>, dev, smem, granted);
+    if (rc != HOGATT_OK) return rc;
+    DenseMaps maps;
+    memset(&maps, 0, sizeof(maps));
+    for (int f = 0; f < args.F; ++f) {
+        if (args.ft.e[f].rows == 0) continue;             // never addressed: no tile lies in an empty fragment
+        rc = fragment_map(args.ft.e[f].k, args.ft.e[f].rows, args.Hkv, dtype, &maps.k[f]);
+        if (rc == HOGATT_OK) rc = fragment_map(args.ft.e[f].v, args.ft.e[f].rows, args.Hkv, dtype, &maps.v[f]);
+        if (rc != HOGATT_OK) return rc;
+    }
+    {   // rotated queries [F, W, Hq, S, E] seen as [F, W, Hkv, G*S, E]; a 128-row block is one box
+        const int gs = args.G * args.S;
+        const cuuint64_t dims[5] = {128, (cuuint64_t)gs, (cuuint64_t)args.Hkv, (cuuint64_t)args.W, (cuuint64_t)args.F};
+        const cuuint32_t box[5] = {64, (cuuint32_t)std::min(gs, kDenseRows), 1, (cuuint32_t)(gs < kDenseRows ? kDenseRows / gs : 1), 1};
+        rc = encode_map(&maps.q, q_rot, dtype, 5, dims, box);
+        if (rc != HOGATT_OK) return rc;
+    }
+    dense_attention_kernel<T><<<dim3(grid), dim3(kDenseThreads), smem, stream>>>(args, maps);
+    HOGATT_CUDA_OK(cudaGetLastError());
+    return HOGATT_OK;
+}
+
+template <class T>
+int launch_all(const KernelArgs& args, const Resolved& r, int dev, int smem_optin, int grid, cudaStream_t stream,
+               const void* q_rot = nullptr) {
     int rc;
-    if (r.kernel == HOGATT_KERNEL_MMA) {
+    if (r.kernel == HOGATT_KERNEL_DENSE) {
+        rc = launch_dense<T>(args, q_rot, std::is_same<T, __half>::value ? HOGATT_F16 : HOGATT_BF16, dev, smem_optin, grid, stream);
+    } else if (r.kernel == HOGATT_KERNEL_MMA) {
         bool ef = r.row_blocks == 1;             // every K/V byte is read once: do not let it displace L2 contents
 #ifdef HOGATT_EXPERIMENT
         if (getenv("HOGATT_STREAM_ONLY")) return launch_mma_dims<T>(args, args.F, args.E, r.mt, dev, smem_optin,
@@ -400,7 +564,8 @@ int launch_all(const KernelArgs& args, const Resolved& r, int dev, int smem_opti
 }
 
 template <>
-int launch_all<float>(const KernelArgs& args, const Resolved& r, int dev, int smem_optin, int grid, cudaStream_t stream) {
+int launch_all<float>(const KernelArgs& args, const Resolved& r, int dev, int smem_optin, int grid, cudaStream_t stream,
+                      const void*) {
     int rc = launch_fma_dims<float>(args, dev, smem_optin, grid, stream);
     if (rc != HOGATT_OK) return rc;
     dim3 mgrid((unsigned)r.units, (unsigned)ceil_div(r.rows_per_block, kMergeWarps));
@@ -412,6 +577,28 @@ int launch_all<float>(const KernelArgs& args, const Resolved& r, int dev, int sm
 }
 
 bool aligned16(const void* p) { return ((uintptr_t)p & 15u) == 0; }
+
+int rope_launch(void* rq, const void* queries, const float* cosines, const float* sines, int F, int W, int Hq, int S, int E,
+                int rotary_dim, int dtype, cudaStream_t stream) {
+    const int64_t rows = (int64_t)F * W * Hq * S;
+    if (rows > (1 << 30)) return HOGATT_ERR_TOO_LARGE;
+    const int64_t work = rows * ((dtype != HOGATT_F32 && E % 8 == 0) ? E / 8 : E);      // chunks or channels
+    const unsigned blocks = (unsigned)std::min<int64_t>((work + 127) / 128, 1 << 16);
+    switch (dtype) {
+        case HOGATT_F32:
+            rope_kernel<float><<<blocks, 128, 0, stream>>>((float*)rq, (const float*)queries, cosines, sines, F, W, Hq, S, E, rotary_dim);
+            break;
+        case HOGATT_F16:
+            rope_kernel<__half><<<blocks, 128, 0, stream>>>((__half*)rq, (const __half*)queries, cosines, sines, F, W, Hq, S, E, rotary_dim);
+            break;
+        case HOGATT_BF16:
+            rope_kernel<__nv_bfloat16><<<blocks, 128, 0, stream>>>((__nv_bfloat16*)rq, (const __nv_bfloat16*)queries, cosines, sines, F, W, Hq, S, E, rotary_dim);
+            break;
+        default: return HOGATT_ERR_UNSUPPORTED_DTYPE;
+    }
+    HOGATT_CUDA_OK(cudaGetLastError());
+    return HOGATT_OK;
+}
 
 int attention_launch(const hogatt_problem* p, bool fused, cudaStream_t stream, const hogatt_peers* peers = nullptr) {
     Resolved r;
@@ -470,11 +657,22 @@ int attention_launch(const hogatt_problem* p, bool fused, cudaStream_t stream, c
     args.ws_m = reinterpret_cast<float*>(ws + w.m);
     args.ws_l = reinterpret_cast<float*>(ws + w.l);
     args.status = p->device_status;
+    args.tune = tune_flags();
+#ifdef HOGATT_TIMELINE
+    {
+        static std::atomic<int> trace_counter{0};
+        args.debug_id = trace_counter.fetch_add(1) % kTraceCalls;
+    }
+#endif
     if (peers) {
         args.world = peers->world;
         args.rank = peers->rank;
         for (int i = 0; i < peers->world; ++i) args.peer_out[i] = peers->out_full[i];
     }
+    // Host plan: only the tensor-core kernel takes one (the FMA kernel always derives its tiles on the device).
+    const bool host_plan = p->host_lengths != nullptr && (r.kernel == HOGATT_KERNEL_MMA || r.kernel == HOGATT_KERNEL_DENSE) &&
+                           !host_plan_disabled();
+    int64_t plan_tiles = 0;
     for (int f = 0; f < p->F; ++f) {
         const int rows = p->fragment_rows[f];
         if (rows < 0) return HOGATT_ERR_BAD_SHAPE;
@@ -483,12 +681,30 @@ int attention_launch(const hogatt_problem* p, bool fused, cudaStream_t stream, c
         args.ft.e[f].k = p->key_fragments[f];
         args.ft.e[f].v = p->value_fragments[f];
         args.ft.e[f].rows = rows;
+        args.ft.e[f].vis = host_plan ? std::max(0, std::min(rows, p->host_lengths[f])) : 0;
+        plan_tiles += ceil_div(args.ft.e[f].vis, r.tile_tokens);
+    }
+    if (host_plan) {
+        if (plan_tiles * r.units > ((int64_t)1 << 40) || plan_tiles > (1 << 30)) return HOGATT_ERR_TOO_LARGE;
+        args.host_plan = 1;
+        args.plan_tiles = (int)plan_tiles;
+        args.plan_ctas = effective_ctas(plan_tiles * r.units, grid);
+        args.stable_fragments = pdl_enabled() ? std::max(0, std::min(p->F, p->stable_fragments)) : 0;
     }
 
+    // The tcgen05 kernel takes its queries already rotated, from memory: the rotated-query output of the call (or
+    // room in the workspace when the caller does not want it) is written by the stand-alone rotation kernel first.
+    const void* q_rot = p->queries;
+    if (r.kernel == HOGATT_KERNEL_DENSE && fused) {
+        void* dst = p->rq ? p->rq : static_cast<void*>(ws + w.rq);
+        rc = rope_launch(dst, p->queries, p->cosines, p->sines, p->F, p->W, p->Hq, p->S, p->E, p->rotary_dim, p->dtype, stream);
+        if (rc != HOGATT_OK) return rc;
+        q_rot = dst;
+    }
     switch (p->dtype) {
-        case HOGATT_F32: rc = launch_all<float>(args, r, dev, smem_optin, grid, stream); break;
-        case HOGATT_F16: rc = launch_all<__half>(args, r, dev, smem_optin, grid, stream); break;
-        case HOGATT_BF16: rc = launch_all<__nv_bfloat16>(args, r, dev, smem_optin, grid, stream); break;
+        case HOGATT_F32: rc = launch_all<float>(args, r, dev, smem_optin, grid, stream, nullptr); break;
+        case HOGATT_F16: rc = launch_all<__half>(args, r, dev, smem_optin, grid, stream, q_rot); break;
+        case HOGATT_BF16: rc = launch_all<__nv_bfloat16>(args, r, dev, smem_optin, grid, stream, q_rot); break;
         default: return HOGATT_ERR_UNSUPPORTED_DTYPE;
     }
     if (rc != HOGATT_OK || !peers) return rc;
@@ -742,24 +958,8 @@ int hogatt_rope_launch(void* rq, const void* queries, const float* cosines, cons
     if (!rq || !queries || !cosines || !sines) return HOGATT_ERR_NULL_POINTER;
     if (F <= 0 || W <= 0 || Hq <= 0 || S <= 0 || E <= 0 || rotary_dim <= 0 || rotary_dim > E || (rotary_dim & 1))
         return HOGATT_ERR_BAD_SHAPE;
-    const int64_t rows = (int64_t)F * W * Hq * S;
-    if (rows > (1 << 30)) return HOGATT_ERR_TOO_LARGE;
-    const int64_t work = rows * ((dtype != HOGATT_F32 && E % 8 == 0) ? E / 8 : E);      // chunks or channels
-    const unsigned blocks = (unsigned)std::min<int64_t>((work + 127) / 128, 1 << 16);
-    switch (dtype) {
-        case HOGATT_F32:
-            rope_kernel<float><<<blocks, 128, 0, stream>>>((float*)rq, (const float*)queries, cosines, sines, F, W, Hq, S, E, rotary_dim);
-            break;
-        case HOGATT_F16:
-            rope_kernel<__half><<<blocks, 128, 0, stream>>>((__half*)rq, (const __half*)queries, cosines, sines, F, W, Hq, S, E, rotary_dim);
-            break;
-        case HOGATT_BF16:
-            rope_kernel<__nv_bfloat16><<<blocks, 128, 0, stream>>>((__nv_bfloat16*)rq, (const __nv_bfloat16*)queries, cosines, sines, F, W, Hq, S, E, rotary_dim);
-            break;
-        default: return HOGATT_ERR_UNSUPPORTED_DTYPE;
-    }
-    HOGATT_CUDA_OK(cudaGetLastError());
-    return HOGATT_OK;
+    if (dtype != HOGATT_F32 && dtype != HOGATT_F16 && dtype != HOGATT_BF16) return HOGATT_ERR_UNSUPPORTED_DTYPE;
+    return rope_launch(rq, queries, cosines, sines, F, W, Hq, S, E, rotary_dim, dtype, stream);
 }
 
 #ifdef HOGATT_TIMELINE
@@ -773,6 +973,20 @@ int hogatt_debug_read_timeline(long long* times /*[2][1024]*/, int* tags /*[2][1
 int hogatt_debug_cta_times(unsigned long long* out /*[3][256]*/, unsigned int* sm /*[256]*/) {
     HOGATT_CUDA_OK(cudaMemcpyFromSymbol(out, g_cta_t, sizeof(unsigned long long) * 768));
     HOGATT_CUDA_OK(cudaMemcpyFromSymbol(sm, g_cta_sm, sizeof(unsigned int) * 256));
+    return HOGATT_OK;
+}
+// out [kTraceCalls][kTraceEvents][256], mout [kTraceCalls][2]; reset != 0 re-arms the merge kernel's min / max slots
+int hogatt_debug_trace(unsigned long long* out, unsigned long long* mout, int reset) {
+    HOGATT_CUDA_OK(cudaMemcpyFromSymbol(out, g_trace, sizeof(g_trace)));
+    HOGATT_CUDA_OK(cudaMemcpyFromSymbol(mout, g_mtrace, sizeof(g_mtrace)));
+    if (reset) {
+        static unsigned long long init[kTraceCalls][2];
+        for (int i = 0; i < kTraceCalls; ++i) {
+            init[i][0] = ~0ull;
+            init[i][1] = 0;
+        }
+        HOGATT_CUDA_OK(cudaMemcpyToSymbol(g_mtrace, init, sizeof(init)));
+    }
     return HOGATT_OK;
 }
 int hogatt_debug_spans(unsigned long long* out8, int reset) {
@@ -897,7 +1111,7 @@ int hogatt_launch_shape(const hogatt_problem* p, int32_t shape[4]) {
     shape[0] = cluster ? HOGATT_KERNEL_MMA_CLUSTER : r.kernel;
     shape[1] = cluster ? r.units * cluster : grid;
     shape[2] = cluster;
-    shape[3] = cluster ? 1 : 2;
+    shape[3] = cluster ? 1 : (r.kernel == HOGATT_KERNEL_DENSE && p->cosines ? 3 : 2);
     return HOGATT_OK;
 }
 

@@ -20,7 +20,7 @@ struct FragmentEntry {                     // 24 bytes: one constant-cache line 
     const void* k;                         // [Hkv, rows, E]
     const void* v;                         // [Hkv, rows, Ev]
     int rows;                              // token extent of the tensors (head stride = rows * E)
-    int pad_;
+    int vis;                               // host plan: upper bound of the visible rows, 0 <= vis <= rows
 };
 struct FragmentTable {
     FragmentEntry e[HOGATT_MAX_FRAGMENTS];
@@ -32,6 +32,12 @@ struct KernelArgs {
     int rows_per_block;    // rows one CTA keeps resident (16 * m-tiles)
     int row_blocks;        // ceil(rows_total / rows_per_block)
     int parts_per_unit;    // partial-result slots reserved per unit in the workspace
+    // Host plan (tensor-core kernel, persistent grid): the tiles come from ft.e[f].vis alone, nothing is read
+    // from device memory to build them; plan_tiles = tiles per unit, plan_ctas = CTAs that get work.
+    int host_plan, plan_tiles, plan_ctas;
+    int stable_fragments;  // fragments [0, stable_fragments) may be fetched before griddepcontrol.wait
+    int debug_id;          // tuning builds only: which slot of the event trace this call writes (0 otherwise)
+    int tune;              // HOGATT_TUNE from the environment (experiments; 0 in normal use)
     float l2scale;         // scale * log2(e): softmax runs in base 2
     void* out;
     void* rq;              // optional rotated-query output
@@ -70,6 +76,12 @@ __device__ int g_timeline_n[2];
 __device__ unsigned long long g_cta_t[3][256];   // per CTA: start, first tile consumed, end (globaltimer ns)
 __device__ unsigned int g_cta_sm[256];
 __device__ unsigned long long g_span[8];      // [0] attn first start, [1] attn last end, [2] merge first start, [3] merge last end
+// Per call (kernel argument debug_id, a counter the host keeps in these builds) and per CTA: globaltimer stamps of
+// named events of the attention kernel, and first start / last end of the merge kernel.
+constexpr int kTraceCalls = 64, kTraceEvents = 8;
+__device__ unsigned long long g_trace[kTraceCalls][kTraceEvents][256];
+__device__ unsigned long long g_mtrace[kTraceCalls][2];
+#define HOGATT_TRACE(id, ev) do { if (blockIdx.x < 256) g_trace[(id) % kTraceCalls][ev][blockIdx.x] = global_timer_ns_(); } while (0)
 #define HOGATT_SPAN_MIN(i) do { if (threadIdx.x == 0) atomicMin(&g_span[i], global_timer_ns_()); } while (0)
 #define HOGATT_SPAN_MAX(i) do { if (threadIdx.x == 0) atomicMax(&g_span[i], global_timer_ns_()); } while (0)
 __device__ __forceinline__ unsigned long long global_timer_ns_() {
@@ -89,6 +101,7 @@ __device__ __forceinline__ unsigned long long global_timer_ns_() {
 #else
 #define HOGATT_TL_DECL
 #define HOGATT_TL(who, tag)
+#define HOGATT_TRACE(id, ev)
 #define HOGATT_SPAN_MIN(i)
 #define HOGATT_SPAN_MAX(i)
 #endif
@@ -264,6 +277,10 @@ __device__ __forceinline__ void bulk_load_hint(uint32_t dst_smem, const void* sr
             "r"(dst_smem),
         "l"(src), "r"(bytes), "r"(bar), "l"(policy)
         : "memory");
+}
+// Ask for `bytes` (a multiple of 16) at `src` to be brought into L2; nothing is waited for.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {
     uint64_t pol;
@@ -457,6 +474,32 @@ __device__ __forceinline__ void build_tile_prefix(const KernelArgs& a, int tile_
         pre[a.F] = acc;
     }
     __syncthreads();
+}
+
+// Host plan: the same two arrays from the kernel arguments alone -- vis[f] is the host's upper bound of the
+// visible rows -- so that nothing is read from device memory before the first K/V copy can be issued.
+// Called by ONE whole warp; the caller synchronises the CTA afterwards.
+__device__ __forceinline__ void host_tile_prefix(const KernelArgs& a, int tile_tokens, int* vis, int* pre) {
+    const int lane = threadIdx.x & 31;
+    int carry = 0;
+#pragma unroll 1
+    for (int f0 = 0; f0 < a.F; f0 += 32) {
+        const int f = f0 + lane;
+        const int v = f < a.F ? a.ft.e[f].vis : 0;
+        const int mine = ceil_div(v, tile_tokens);
+        int x = mine;                                      // inclusive scan over the warp
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int y = __shfl_up_sync(0xffffffffu, x, o);
+            if (lane >= o) x += y;
+        }
+        if (f < a.F) {
+            vis[f] = v;
+            pre[f] = carry + x - mine;
+        }
+        carry += __shfl_sync(0xffffffffu, x, 31);
+    }
+    if (lane == 0) pre[a.F] = carry;
 }
 
 // Row bookkeeping: query row r of a kv head (0 <= r < W*G*S) is worker w, group head g, token s

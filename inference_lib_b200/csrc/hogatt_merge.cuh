@@ -138,14 +138,20 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const __grid_co
     const int u = blockIdx.x;
     const int rb = u / a.Hkv, hkv = u % a.Hkv;
     HOGATT_SPAN_MIN(2);
-    pdl_trigger();       // the next call's attention kernel may queue up behind this grid
+#ifdef HOGATT_TIMELINE
+    if (threadIdx.x == 0) atomicMin(&g_mtrace[a.debug_id % kTraceCalls][0], global_timer_ns_());
+#endif
+    if (!(a.tune & 1)) pdl_trigger();       // the next call's attention kernel may queue up behind this grid
     pdl_wait();          // partials are complete and visible once the attention grid has finished
+    if (a.tune & 1) pdl_trigger();
     const int units = a.row_blocks * a.Hkv;
     const int RPB = a.rows_per_block, Ev = a.Ev;
     // how many CTAs left a partial for this unit: from the header the attention kernel wrote
+    // (under a host plan both numbers are kernel arguments)
     const int* hdr = a.header;
+    const int host_plan = a.host_plan, plan_tiles = a.plan_tiles, plan_ctas = a.plan_ctas;
     auto count_of = [=]() {
-        const int TH = __ldcg(hdr), ctas = __ldcg(hdr + 1);
+        const int TH = host_plan ? plan_tiles : __ldcg(hdr), ctas = host_plan ? plan_ctas : __ldcg(hdr + 1);
         int first = 0, count = 0;
         if (TH > 0) unit_ctas(u, TH, (int64_t)units * TH, ctas, &first, &count);
         return count;
@@ -167,6 +173,9 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const __grid_co
                                           count_of, bases, nbases, offset, lane, e0);
     }
     HOGATT_SPAN_MAX(3);
+#ifdef HOGATT_TIMELINE
+    if (threadIdx.x == 0) atomicMax(&g_mtrace[a.debug_id % kTraceCalls][1], global_timer_ns_());
+#endif
 }
 
 // Completion exchange of the fused output all-gather: one warp, lane p talks to rank p.

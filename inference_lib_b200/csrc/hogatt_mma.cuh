@@ -60,7 +60,11 @@ struct MmaCfg {
     // that to ~100 GB/s per SM.  With a CTA on every SM the chip's HBM gives each SM 44 GB/s, and the
     // second producer measured 0.5-1 us SLOWER per call there; it only pays when few SMs stream a lot.
     static constexpr int NPW = 1;
-    static constexpr int THREADS = (NCW + NPW) * 32;
+    // Helper warp (decode-sized query blocks only): writes the rotated-query side output, so that neither the
+    // producer (whose copies would stall behind those loads and stores) nor the consumers (whose first tile would)
+    // has to.  Ten warps would cut the register budget of the 64-row variant, which writes it with its consumers.
+    static constexpr int NHW = (MT <= 2) ? 1 : 0;
+    static constexpr int THREADS = (NCW + NPW + NHW) * 32;
     static constexpr int RPB = 16 * MT;                  // query rows per CTA
     static constexpr int SLOT_FLOATS = NT_O * 4 * 32;    // one warp's accumulators
     static constexpr int QPITCH = ROWB + 16;             // bytes per staged query row (padding: conflict-free ldmatrix)
@@ -124,6 +128,14 @@ struct OutputTargets {
     }
 };
 
+// Rows of fragment f that a query may see at all: under a device plan vis[f] is exact already; under a host plan
+// vis[f] is only the host's bound, and the true length comes from the tensors' extent and the device-side lengths.
+__device__ __forceinline__ int visible_length(const KernelArgs& a, int f, const int* vis) {
+    int v = vis[f];
+    if (a.host_plan && a.flen) v = min(v, a.flen[f]);
+    return v;
+}
+
 // CL = false: persistent grid over balanced tile ranges, partials to the workspace, merge_kernel follows.
 // CL = true : launched in thread-block clusters, one cluster per (kv head, row block) unit; CTA `rank`
 //             of the cluster takes tiles [rank*TH/CS, (rank+1)*TH/CS) of the unit; every warp leaves its
@@ -149,6 +161,7 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
     HOGATT_TL_DECL;
     HOGATT_TL(warp == 0 ? 0 : 1, 1);
     HOGATT_SPAN_MIN(0);
+    if (tid == 0) HOGATT_TRACE(a.debug_id, 0);
 #ifdef HOGATT_TIMELINE
     if (tid == 0) {
         g_cta_t[0][blockIdx.x] = global_timer_ns_();
@@ -170,9 +183,27 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_proxy_async_smem();
     }
-    pdl_wait();          // everything above touched only this CTA's shared memory
-    pdl_trigger();       // the merge kernel may take its place on the SMs now; it waits for this grid itself
-    build_tile_prefix(a, C::TILE, vis, pre);     // ends with __syncthreads(): barriers are visible too
+    // Programmatic dependent launch: this grid may have been scheduled while the stream's preceding kernel is
+    // still running.  `waited` says whether this thread has passed griddepcontrol.wait, i.e. may touch global
+    // memory that earlier work writes or reads (everything except the K/V rows of "stable" fragments).
+    const bool is_helper = C::NHW != 0 && warp == C::NCW + C::NPW;
+    const bool is_producer = warp == 0 || (warp > C::NCW && !is_helper);
+    bool waited;
+    if (a.host_plan) {
+        // The tile plan comes from the kernel arguments: nothing is read from device memory before the first
+        // K/V copy.  Every thread waits where it first needs global memory that earlier work may write: the
+        // consumers in their first fragment prologue (queries, tables, locations), the producer when it reaches a
+        // tile that it may not fetch early (or has filled the ring and sent the rest of its stable tiles to L2).
+        if (warp == 0) host_tile_prefix(a, C::TILE, vis, pre);
+        __syncthreads();                         // barriers and plan are visible
+        waited = false;
+    } else {
+        pdl_wait();      // everything above touched only this CTA's shared memory
+        pdl_trigger();   // the merge kernel may take its place on the SMs now; it waits for this grid itself
+        build_tile_prefix(a, C::TILE, vis, pre);     // ends with __syncthreads(): barriers are visible too
+        waited = true;
+        if (tid == 32) HOGATT_TRACE(a.debug_id, 1);
+    }
     if (warp <= 1) HOGATT_TL(warp, 2);
 
     const int TH = pre[a.F];
@@ -180,24 +211,22 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
     const int64_t N = (int64_t)units * TH;
     const int ctas = CL ? (int)gridDim.x : effective_ctas(N, gridDim.x);
     const int CS = CL ? (int)cluster_nctarank() : 1, crank = CL ? (int)cluster_ctarank() : 0;
-    if (!CL && blockIdx.x == 0 && tid == 0) {
+    if (!CL && !a.host_plan && blockIdx.x == 0 && tid == 0) {      // (host plan: the merge kernel has both as arguments)
         a.header[0] = TH;
         a.header[1] = ctas;
     }
     // The rotated-query output is a side product every CTA writes a share of.  When it is small (a few
-    // 16-byte chunks per thread: decode) and the grid is the persistent one, warp 0 -- the producer -- writes it
-    // once the K/V ring is full and it would only wait anyway, which keeps those loads off the consumers'
-    // start-up path (measured -0.9 us per call; doing it after the producer's last tile instead delays the CTA's
-    // exit and gives the gain back).  When it is large (many query tokens) the consumer threads write it after
-    // their first fragment prologue, while the first K/V tile is still in flight, with far more loads in flight
-    // than one warp could keep; so do cluster launches, whose CTAs have too few tiles each to hide a producer
-    // that is busy elsewhere (measured +1...2 us with the producer writing it).
+    // 16-byte chunks per thread: decode) the helper warp writes it, which keeps those loads and stores off the
+    // consumers' start-up path and off the producer's copy stream.  When it is large (many query tokens) the
+    // consumer threads write it after their first fragment prologue, while the first K/V tile is still in flight,
+    // with far more loads in flight than one warp could keep.
     const bool want_rq = a.rq != nullptr && a.cos != nullptr;
-    const bool rq_by_producer =
-        !CL && want_rq && (int64_t)a.F * a.W * a.Hq * a.S * (HD / 8) <= (int64_t)4 * gridDim.x * 32;
-    const bool rq_by_consumers = want_rq && !rq_by_producer;
+    const bool rq_by_helper =
+        C::NHW != 0 && want_rq && (int64_t)a.F * a.W * a.Hq * a.S * (HD / 8) <= (int64_t)8 * gridDim.x * 32;
+    const bool rq_by_consumers = want_rq && !rq_by_helper;
     if ((int)blockIdx.x >= ctas) {
-        if (rq_by_producer && warp == 0)
+        if (!waited) pdl_wait();
+        if (rq_by_helper && is_helper)
             write_rotated_queries<T>(a.q, a.rq, a.cos, a.sin, a.F, a.W, a.Hq, a.S, HD, a.R, blockIdx.x * 32 + lane,
                                      gridDim.x * 32);
         if (rq_by_consumers && warp > 0 && warp <= C::NCW)
@@ -217,10 +246,22 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
         t1 = cta_first_tile(blockIdx.x + 1, N, ctas);
     }
 
+    if (is_helper) {
+        if (!waited) pdl_wait();
+        if (rq_by_helper)
+            write_rotated_queries<T>(a.q, a.rq, a.cos, a.sin, a.F, a.W, a.Hq, a.S, HD, a.R, blockIdx.x * 32 + lane,
+                                     gridDim.x * 32);
+        if constexpr (CL) {
+            cluster_sync_all();
+            cluster_sync_all();
+        }
+        return;
+    }
+
     // =====================================================================================
     // Producer warp
     // =====================================================================================
-    if (warp == 0 || warp > C::NCW) {
+    if (is_producer) {
         constexpr int COPIES = 16 / C::NPW;              // bulk copies per producer warp per stage (8 K groups + 8 V groups in all)
         const int copy0 = warp == 0 ? 0 : COPIES;
         uint64_t policy = 0;
@@ -237,6 +278,32 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
             const int ntok = min(C::TILE, vis[f] - tok0);
             const int stage = it % C::NSTAGE;
             const uint32_t phase = (uint32_t)(it / C::NSTAGE) & 1u;
+            if (!waited && (it >= C::NSTAGE || f >= a.stable_fragments)) {
+                if (f < a.stable_fragments && lane < 2) {
+                    // The ring is full.  Before waiting, ask for the rest of this CTA's stable tiles to be brought
+                    // into L2 (lane 0: keys, lane 1: values): HBM works while the preceding kernel finishes.
+                    int64_t u2 = u;
+                    int j2 = j, f2 = fscan;
+#pragma unroll 1
+                    for (int64_t t2 = t; t2 < t1 && t2 < t + 24; ++t2) {
+                        while (j2 >= pre[f2 + 1]) ++f2;
+                        if (f2 >= a.stable_fragments) break;
+                        const int tk = (j2 - pre[f2]) * C::TILE;
+                        const int nt = min(C::TILE, vis[f2] - tk);
+                        const unsigned char* src = static_cast<const unsigned char*>(lane ? a.ft.e[f2].v : a.ft.e[f2].k) +
+                                                   ((size_t)(u2 % a.Hkv) * a.ft.e[f2].rows + tk) * C::ROWB;
+                        bulk_prefetch_l2(src, (uint32_t)nt * C::ROWB);
+                        if (++j2 == TH) {
+                            j2 = 0;
+                            ++u2;
+                            f2 = 0;
+                        }
+                    }
+                }
+                pdl_wait();                      // from here on: fragments that earlier work of the stream may have written
+                waited = true;
+                if (tid == 0) HOGATT_TRACE(a.debug_id, 5);
+            }
             ok = mbar_wait_bounded(empty0 + 8 * stage, phase ^ 1u, abort_flag, a.status, STATUS_WAIT_EMPTY_TIMEOUT);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
@@ -258,18 +325,15 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
                 }
             }
             HOGATT_TL(0, 100 + it);
-            if (rq_by_producer && warp == 0 && it + 1 == (int)min((int64_t)C::NSTAGE, t1 - t0))
-                write_rotated_queries<T>(a.q, a.rq, a.cos, a.sin, a.F, a.W, a.Hq, a.S, HD, a.R, blockIdx.x * 32 + lane,
-                                         gridDim.x * 32);
+            if (tid == 0 && it == 0) HOGATT_TRACE(a.debug_id, 4);
             if (++j == TH) {
                 j = 0;
                 ++u;
                 fscan = 0;
             }
         }
-        if (rq_by_producer && warp == 0 && t0 == t1)         // (a CTA without tiles; cannot happen on the persistent grid)
-            write_rotated_queries<T>(a.q, a.rq, a.cos, a.sin, a.F, a.W, a.Hq, a.S, HD, a.R, blockIdx.x * 32 + lane,
-                                     gridDim.x * 32);
+        if (!waited) pdl_wait();
+        if (tid == 0) HOGATT_TRACE(a.debug_id, 6);
         // Do not leave while copies may still be landing in this CTA's shared memory.
         if (lane == 0) {
             const int pending = min(it, C::NSTAGE);
@@ -297,7 +361,7 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
     float o[C::NT_O][4];
     float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
     uint32_t qf[C::KSTEPS][4];
-    int lim_a = 0, lim_b = 0;
+    int lim_a = 0, lim_b = 0, wlim = 0;      // wlim: the largest limit of any row of this warp
     RowId id_a = {0, 0, 0}, id_b = {0, 0, 0};
     bool valid_a = false, valid_b = false;
     uint32_t cphase = 0;
@@ -335,11 +399,20 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
         const int f = fscan;
         if (f != cur_f) {
             cur_f = f;
+            if (!waited) {
+                pdl_wait();
+                waited = true;
+                if (tid == 32) HOGATT_TRACE(a.debug_id, 1);
+                // Only now may the next kernel of the stream be scheduled behind this grid (it is, once every CTA has
+                // said so): whatever it does before its own wait can then overlap with this call's kernels only,
+                // never with work that was enqueued before this call.
+                pdl_trigger();
+            }
             // ---- per-fragment prologue ----------------------------------------------------------
             // All consumer threads rotate the block's query rows for this fragment (16-byte chunks,
             // every load independent: one memory round trip), round them to the storage type and
             // stage them in shared memory; each warp then pulls its MMA A-fragments with ldmatrix.
-            const int vf = vis[f];
+            const int vf = visible_length(a, f, vis);
             const unsigned char* qsrc = qtile;
             if (C::Q2BYTES != 0 && pre_u == cur_u && pre_f == f) {
                 // staged at kernel start: nothing to load (the tile has been complete since the second
@@ -404,7 +477,7 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
                     }
                     if (seg && ctid < C::RPB) {                // visibility limits of the pre-staged segment
                         const int gr = srb * C::RPB + ctid;
-                        const int v2 = vis[sf];
+                        const int v2 = visible_length(a, sf, vis);
                         int lim = v2;
                         if (gr < a.rows_total) {
                             const RowId id = decode_row(gr, a.G, a.S);
@@ -423,9 +496,13 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
                 if (warp == 1) HOGATT_TL(1, 21);
                 if (!consumer_sync()) break;                   // the query tile is complete
                 if (warp == 1) HOGATT_TL(1, 22);
+                if (tid == 32 && it == 0) HOGATT_TRACE(a.debug_id, 7);
                 lim_a = valid_a ? min(loc_a, vf - 1) + 1 : vf;
                 lim_b = valid_b ? min(loc_b, vf - 1) + 1 : vf;
             }
+            wlim = max(lim_a, lim_b);
+#pragma unroll
+            for (int sh = 16; sh > 0; sh >>= 1) wlim = max(wlim, __shfl_xor_sync(0xffffffffu, wlim, sh));
             {
                 const uint32_t qaddr = smem_u32(qsrc) + (mt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * C::QPITCH + (lane >> 4) * 16;
 #pragma unroll
@@ -450,6 +527,7 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
 #ifdef HOGATT_TIMELINE
         if (warp == 1 && lane == 0 && it == 0) g_cta_t[1][blockIdx.x] = global_timer_ns_();
 #endif
+        if (tid == 32 && it == 0) HOGATT_TRACE(a.debug_id, 2);
 #ifdef HOGATT_EXPERIMENT
         if (use_evict_first & 2) {           // stream only: hand the stage straight back (results are garbage)
             __syncwarp();
@@ -463,14 +541,17 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
 #endif
 
         const int i0 = slice * C::NT_S;      // first in-group position of this warp's slice
-        if (ntok < C::TILE) {
-            // V rows past the end of a short tile were not written by the copy: make them finite
-            // (their probabilities are exactly zero, but 0 * NaN would poison the sums).
+        // Keys from `nvalid` on are masked for every row of this warp: their probabilities are exactly zero, but
+        // 0 * NaN would poison the sums, and their V rows may hold anything -- past the end of a short tile the
+        // copy wrote nothing, and under a host plan rows between a fragment's true length and the host's bound
+        // are fetched as they are.  Make those V rows (of this warp's own slice) finite.
+        const int nvalid = min(ntok, wlim - tok0);
+        if (nvalid < C::TILE) {
             unsigned char* vgen = stages + (size_t)stage * C::STAGE_BYTES + C::KV_BYTES;
 #pragma unroll 1
             for (int r = 0; r < 8 * C::NT_S; ++r) {
                 const int g = r & 7, i = i0 + (r >> 3);
-                if (g * C::GT + i >= ntok && lane < C::ROWB / 16)
+                if (g * C::GT + i >= nvalid && lane < C::ROWB / 16)
                     *reinterpret_cast<int4*>(vgen + g * C::GROUP_STRIDE + i * C::ROWB + lane * 16) = make_int4(0, 0, 0, 0);
             }
             __syncwarp();
@@ -636,7 +717,7 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
 
         if (warp == 1 && last) HOGATT_TL(1, 900);
         // ---- hand the stage back to the producer ----
-        if (wrote_scratch || ntok < C::TILE) fence_proxy_async_smem();
+        if (wrote_scratch || nvalid < C::TILE) fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) mbar_arrive(empty0 + 8 * stage);
 
@@ -647,6 +728,10 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
     }
     if constexpr (CL) {
         constexpr int CTHREADS = C::NCW * 32;
+        if (!waited) {                   // a CTA without tiles
+            pdl_wait();
+            pdl_trigger();
+        }
         if (rq_by_consumers && it == 0)  // a CTA without tiles still writes its share of the rotated queries
             write_rotated_queries<T>(a.q, a.rq, a.cos, a.sin, a.F, a.W, a.Hq, a.S, HD, a.R,
                                      blockIdx.x * CTHREADS + tid - 32, gridDim.x * CTHREADS);
@@ -771,6 +856,7 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
         if (warp == 1) HOGATT_TL(1, 902);
         cluster_sync_all();              // no CTA leaves while another may still read its shared memory
     }
+    if (tid == 32) HOGATT_TRACE(a.debug_id, 3);
 #ifdef HOGATT_TIMELINE
     if (warp == 1 && lane == 0) {
         atomicMax(&g_span[1], global_timer_ns_());

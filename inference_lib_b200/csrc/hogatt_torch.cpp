@@ -12,6 +12,7 @@
 #include <c10/cuda/CUDAStream.h>
 #include <torch/library.h>
 
+#include <algorithm>
 #include <vector>
 
 #include "../../include/hogatt.h"
@@ -36,7 +37,8 @@ void check_status(int rc, const char* what) {
 void run_attention(at::Tensor& out, at::Tensor* rq, double scale, const at::Tensor& locations,
                    const at::Tensor& queries, const at::Tensor& fragment_lengths,
                    const std::vector<at::Tensor>& key_fragments, const std::vector<at::Tensor>& value_fragments,
-                   const at::Tensor* cosines, const at::Tensor* sines) {
+                   const at::Tensor* cosines, const at::Tensor* sines, const std::vector<int64_t>* host_lengths = nullptr,
+                   int64_t stable_fragments = 0) {
     const bool fused = cosines != nullptr;
     TORCH_CHECK(out.is_cuda(), "libhogatt: tensors must live on a CUDA device");
     const c10::cuda::CUDAGuard guard(out.device());
@@ -46,6 +48,7 @@ void run_attention(at::Tensor& out, at::Tensor* rq, double scale, const at::Tens
     TORCH_CHECK(locations.dim() == 3 && locations.is_contiguous() && locations.scalar_type() == at::kInt,
                 "locations must be contiguous int32 [F,W,S]");
     const int F = locations.size(0);
+    TORCH_CHECK(F > 0, "libhogatt: at least one fragment is needed");
     TORCH_CHECK_EQ(locations.size(1), W);
     TORCH_CHECK_EQ(locations.size(2), S);
 
@@ -72,8 +75,11 @@ void run_attention(at::Tensor& out, at::Tensor* rq, double scale, const at::Tens
     TORCH_CHECK_EQ((int64_t)key_fragments.size(), (int64_t)F);
     TORCH_CHECK_EQ((int64_t)value_fragments.size(), (int64_t)F);
 
+    for (const at::Tensor* t : {&locations, &queries, &fragment_lengths, cosines, sines, (const at::Tensor*)rq})
+        TORCH_CHECK(t == nullptr || t->device() == out.device(), "libhogatt: every tensor must be on the output's device");
+
     std::vector<const void*> kptr(F), vptr(F);
-    std::vector<int32_t> rows(F);
+    std::vector<int32_t> rows(F), bound(F);
     const int fo = key_fragments[0].dim() == 4 ? 1 : 0;
     const int Hkv = key_fragments[0].size(fo);
     for (int f = 0; f < F; ++f) {
@@ -92,6 +98,10 @@ void run_attention(at::Tensor& out, at::Tensor* rq, double scale, const at::Tens
         kptr[f] = k.const_data_ptr();
         vptr[f] = v.const_data_ptr();
         rows[f] = (int32_t)k.size(fo + 1);
+        // What the host knows about the fragment's length: the reference's callers pass tensors that end at the
+        // fragment's length (python/hogwild/attention.py:26-35, :160-162), so without better knowledge the row
+        // count is the bound; a caller that keeps fragments in larger slabs passes its own numbers.
+        bound[f] = host_lengths ? (int32_t)std::max<int64_t>(0, std::min<int64_t>((*host_lengths)[f], rows[f])) : rows[f];
     }
 
     hogatt_problem p = {};
@@ -105,6 +115,8 @@ void run_attention(at::Tensor& out, at::Tensor* rq, double scale, const at::Tens
     p.key_fragments = kptr.data();
     p.value_fragments = vptr.data();
     p.fragment_rows = rows.data();
+    p.host_lengths = bound.data();
+    p.stable_fragments = (int32_t)std::max<int64_t>(0, std::min<int64_t>(stable_fragments, F));
     if (fused) {
         TORCH_CHECK(cosines->dim() == 4 && sines->dim() == 4 && cosines->is_contiguous() && sines->is_contiguous() &&
                         cosines->scalar_type() == at::kFloat && sines->scalar_type() == at::kFloat,
@@ -189,6 +201,20 @@ void hogwild_fused(at::Tensor& out, at::Tensor& rotated_queries, double scale, c
         vals.push_back(value_fragments[i].contiguous());
     }
     run_attention(out, &rotated_queries, scale, locations, queries, fragment_lengths, keys, vals, &cosines, &sines);
+}
+
+// hogwild_fused for callers that keep every fragment in a preallocated slab [Hkv, capacity, E] (no copies are
+// made here, the slabs must be contiguous) and know on the host how long each fragment can be at most:
+// `host_lengths[f]` bounds the visible rows of fragment f, `stable_fragments` leading fragments are not written
+// by work enqueued before this call (see hogatt_problem in include/hogatt.h).  No counterpart in the reference.
+void hogwild_fused_planned(at::Tensor& out, at::Tensor& rotated_queries, double scale, const at::Tensor& locations,
+                           const at::Tensor& queries, const at::Tensor& fragment_lengths,
+                           const std::vector<at::Tensor>& key_fragments, const std::vector<at::Tensor>& value_fragments,
+                           const at::Tensor& cosines, const at::Tensor& sines, const std::vector<int64_t>& host_lengths,
+                           int64_t stable_fragments) {
+    TORCH_CHECK_EQ((int64_t)host_lengths.size(), (int64_t)key_fragments.size());
+    run_attention(out, &rotated_queries, scale, locations, queries, fragment_lengths, key_fragments, value_fragments,
+                  &cosines, &sines, &host_lengths, stable_fragments);
 }
 
 // --- paged operators (src/binding.cu:269-322) --------------------------------------------------------
@@ -340,6 +366,10 @@ TORCH_LIBRARY(libhogatt, m) {
           "Tensor block_table, Tensor seq_lengths) -> ()", tags, torch::_RegisterOrVerify::REGISTER);
     m.def("hogwild_varlen_paged_sdpa(Tensor(a!) output, float scale, Tensor locations, Tensor queries, "
           "Tensor fragment_lengths, Tensor key_cache, Tensor value_cache, Tensor block_table, Tensor cu_seqlens_q, Tensor cu_seqlens_k) -> ()", tags, torch::_RegisterOrVerify::REGISTER);
+    // beyond the reference's six operators: hogwild_fused with the host's knowledge of the fragment lengths
+    m.def("hogwild_fused_planned(Tensor(a!) output, Tensor(b!) rq, float scale, Tensor locations, Tensor queries, "
+          "Tensor fragment_lengths, Tensor[] key_fragments, Tensor[] value_fragments, Tensor cosines, Tensor sines, "
+          "int[] host_lengths, int stable_fragments) -> ()", tags, torch::_RegisterOrVerify::REGISTER);
 }
 
 TORCH_LIBRARY_IMPL(libhogatt, CUDA, m) {
@@ -349,4 +379,5 @@ TORCH_LIBRARY_IMPL(libhogatt, CUDA, m) {
     m.impl("hogwild_paged_sdpa", hogwild_paged_attention);
     m.impl("copy_to_blocks", copy_to_blocks);
     m.impl("hogwild_varlen_paged_sdpa", hogwild_varlen_paged_attention);
+    m.impl("hogwild_fused_planned", hogwild_fused_planned);
 }

@@ -66,6 +66,7 @@ class HogwildAttention(nn.Module):
         if self._rq is None or self._rq.shape != (F, W, self.num_heads, S, self.head_dim):
             self._rq = torch.empty((F, W, self.num_heads, S, self.head_dim), dtype=q.dtype, device=q.device)
             self._att = torch.empty((W, self.num_heads, S, cs.values[0].shape[-1]), dtype=q.dtype, device=q.device)
-        att = ops.hogwild_fused(q, cs.loc, cs.keys, cs.values, self.scaling, cs.frags, cs.cos, cs.sin,
-                                rotated_queries=self._rq, out=self._att)
+        att = ops.hogwild_fused_planned(q, cs.loc, cs.keys, cs.values, self.scaling, cs.frags, cs.cos, cs.sin,
+                                        rotated_queries=self._rq, out=self._att, host_lengths=cs.host_lengths,
+                                        stable_fragments=cs.stable)
         return self.o_proj(att.transpose(1, 2).reshape(W, S, -1))

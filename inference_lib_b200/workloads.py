@@ -239,6 +239,17 @@ EDGE_CASES: Dict[str, Dict] = {
     "split_many_bf16": dict(W=2, Hq=8, Hkv=2, E=128, S=1, lengths=[20000, 3000, 3001], theta=5e5,
                             dtype=torch.bfloat16),
     "split_many_f32": dict(W=2, Hq=4, Hkv=2, E=64, S=1, lengths=[6000, 700, 701], theta=1e4, dtype=torch.float32),
+    # many query rows per kv head (token chunks): 128-row query blocks.  G*S = 128: a block is one worker ...
+    "dense_chunk_bf16": dict(W=2, Hq=16, Hkv=2, E=128, S=16, lengths=[300, 40, 150], theta=5e5, dtype=torch.bfloat16),
+    # ... G*S = 32: a block is four workers ...
+    "dense_small_gs_bf16": dict(W=8, Hq=8, Hkv=2, E=128, S=8, lengths=[200, 20, 21, 22, 23, 24, 25, 26, 129], theta=5e5,
+                                dtype=torch.bfloat16),
+    # ... G*S = 256: a worker is two blocks (fp16) ...
+    "dense_big_gs_f16": dict(W=2, Hq=16, Hkv=1, E=128, S=16, lengths=[260, 33, 47], theta=1e4, dtype=torch.float16),
+    # ... and 192 rows: the second block is half empty; one fragment is invisible to worker 0, one is empty
+    "dense_partial_block_bf16": dict(W=3, Hq=8, Hkv=2, E=128, S=16, lengths=[131, 17, 64, 0, 30], theta=5e5,
+                                     dtype=torch.bfloat16,
+                                     orders=[[0, 2, 4, 1], [0, 1, 4, 2], [0, 1, 2, 4]]),
 }
 
 

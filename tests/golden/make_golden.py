@@ -1,8 +1,8 @@
 """Generate golden outputs by running the REFERENCE's own PyTorch path.
 
-Run in the build container only (it needs the reference checkout; nothing at test time does):
+Needs a checkout of the reference (nothing at test time does):
 
-    python tests/golden/make_golden.py [--reference /path/to/reference] [--only name,name]
+    python tests/golden/make_golden.py --reference /path/to/reference [--only name,name]
 
 For every seeded problem of ``inference_lib_b200.workloads`` it calls the reference's
 ``apply_rotary_pos_emb`` + ``hogwild_sdpa_pt(..., return_intermediate_results=True)``
@@ -10,7 +10,7 @@ For every seeded problem of ``inference_lib_b200.workloads`` it calls the refere
 result in ``tests/golden/reference_outputs.npz``:
 
 * ``<name>/out``  fp32 ``[W,Hq,S,Ev]`` (for cfg5, whose output is 4 MiB per group, the rows
-  ``[:, ::8, ::4, :]`` only; four groups, seeds 0..3)
+  ``[:, ::8, ::4, :]`` only; four groups, seeds 0..3; every row of group 0 goes to ``cfg5_g0_full.npz``)
 * ``<name>/rq``   rotated queries ``[F,W,Hq,S,E]`` as fp32, for a few small problems
 
 The reference module imports as shipped except for one thing: it looks up an installed
@@ -68,7 +68,8 @@ def reference_run(ref, p: wl.Problem):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("HOGWILD_REFERENCE"), required="HOGWILD_REFERENCE" not in os.environ,
+                    help="checkout of choyakawa/inference_lib (or set HOGWILD_REFERENCE)")
     ap.add_argument("--only", default="")
     ap.add_argument("--skip-big", action="store_true", help="skip cfg4 (20 s, ~10 GB RSS)")
     args = ap.parse_args()
@@ -89,6 +90,8 @@ def main():
         p = build()
         out, rq = reference_run(ref, p)
         out = out.to(torch.float32)
+        if name == "cfg5_g0":
+            np.savez_compressed(os.path.join(HERE, "cfg5_g0_full.npz"), out=out.contiguous().numpy())
         if name.startswith("cfg5"):
             out = out[CFG5_SLICE]
         store[f"{name}/out"] = out.contiguous().numpy()

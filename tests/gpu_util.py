@@ -7,7 +7,9 @@ import torch
 from inference_lib_b200 import _cabi
 from inference_lib_b200 import workloads as wl
 
-CANARY = 0x5A
+CANARY = 0x5A          # around the buffers: any overrun shows
+WS_FILL = 0xFF         # inside the workspace: every fp32 word is a NaN, so a slot that is read without having been
+                       # written (or multiplied by zero instead of being selected away) poisons the result
 
 
 class Result:
@@ -16,10 +18,12 @@ class Result:
 
 
 def run_cabi(p: wl.Problem, *, fused: bool = True, want_rq: bool = False, kernel=_cabi.KERNEL_AUTO, max_ctas: int = 0,
-             device: str = "cuda:0", pre_rotated=None) -> Result:
+             device: str = "cuda:0", pre_rotated=None, host_lengths=None, stable_fragments: int = 0, keys=None,
+             values=None) -> Result:
     """One call through ``hogatt_fused_launch`` / ``hogatt_sdpa_launch`` with canaries around the
     output and the workspace.  ``p`` holds CPU tensors; ``pre_rotated`` is the [F,W,Hq,S,E] query
-    tensor for the sdpa entry point."""
+    tensor for the sdpa entry point; ``keys`` / ``values`` replace the problem's device fragments
+    (already on the device); ``host_lengths`` / ``stable_fragments`` as in ``_cabi.bind``."""
     dev = torch.device(device)
     d = p.to(dev)
     W, Hq, S, Ev = p.W, p.Hq, p.S, p.Ev
@@ -32,14 +36,16 @@ def run_cabi(p: wl.Problem, *, fused: bool = True, want_rq: bool = False, kernel
         q, cos, sin = d.queries, d.cos, d.sin
     else:
         q, cos, sin = pre_rotated.to(dev).contiguous(), None, None
-    bp = _cabi.bind(out=out, queries=q, locations=d.locations, keys=d.keys, values=d.values, scale=p.scale,
+    bp = _cabi.bind(out=out, queries=q, locations=d.locations, keys=keys if keys is not None else d.keys,
+                    values=values if values is not None else d.values, scale=p.scale,
                     fragment_lengths=d.fragment_lengths, cos=cos, sin=sin, rq=rq, status=status, kernel=kernel,
-                    max_ctas=max_ctas)
+                    max_ctas=max_ctas, host_lengths=host_lengths, stable_fragments=stable_fragments)
     need = _cabi.workspace_bytes(bp)
     assert need > 0, "library refused the problem"
     ws_buf = torch.full((need + 512,), CANARY, dtype=torch.uint8, device=dev)
     off = (-ws_buf.data_ptr()) % 256
     ws = ws_buf[off:off + need]
+    ws.fill_(WS_FILL)
     bp.struct.workspace, bp.struct.workspace_bytes = ws.data_ptr(), need
     rc = _cabi.launch(bp, torch.cuda.current_stream(dev).cuda_stream)
     torch.cuda.synchronize(dev)

@@ -35,8 +35,9 @@ def test_status_strings(lib):
 
 
 def test_struct_layout_matches_the_header(lib):
-    # 10 x 4-byte scalars, 7 pointers, 3 host-array pointers, workspace ptr + size, status ptr, 2 ints
-    assert C.sizeof(_cabi.Problem) == 40 + 8 * 7 + 8 * 3 + 16 + 8 + 8
+    # 10 x 4-byte scalars, 7 pointers, 3 host-array pointers, workspace ptr + size, status ptr, 2 ints,
+    # host_lengths pointer, stable_fragments + one reserved int
+    assert C.sizeof(_cabi.Problem) == 40 + 8 * 7 + 8 * 3 + 16 + 8 + 8 + 8 + 8
 
 
 def _describe(lib, visible, sms=148, **dims):
@@ -65,6 +66,9 @@ def test_plan_for_the_headline_shapes(lib):
     rc, plan = _describe(lib, [256, 64, 64], F=3, W=2, Hq=8, Hkv=2, E=64, Ev=64, S=1, dtype=_cabi.F32)
     assert rc == 0 and plan[7] == _cabi.KERNEL_FMA and plan[0] == 32
     rc, plan = _describe(lib, [16384] + [1024] * 8, F=9, W=8, Hq=64, Hkv=8, E=128, Ev=128, S=16, dtype=_cabi.BF16)
+    # 1,024 query rows per kv head: the tcgen05 kernel, 128-row blocks, 192 tiles of 128 keys per unit
+    assert rc == 0 and plan[7] == _cabi.KERNEL_DENSE and plan[0] == 128 and plan[1] == 128 and plan[2] == 8 and plan[3] == 192 and plan[4] == 64
+    rc, plan = _describe(lib, [16384] + [1024] * 8, F=9, W=8, Hq=64, Hkv=8, E=128, Ev=128, S=16, dtype=_cabi.BF16, kernel=_cabi.KERNEL_MMA)
     assert rc == 0 and plan[1] == 64 and plan[2] == 16 and plan[4] == 128
 
 

@@ -57,7 +57,7 @@ def test_one_workspace_serves_many_launches_and_shapes(golden):
     names = ["cfg2", "target", "ragged_bf16", "cfg3", "cfg2", "gqa5_bf16", "target"]
     dev = torch.device("cuda:0")
     stream = torch.cuda.current_stream(dev).cuda_stream
-    ws = torch.full((64 << 20,), 0x5A, dtype=torch.uint8, device=dev)
+    ws = torch.full((64 << 20,), 0xFF, dtype=torch.uint8, device=dev)       # NaN in every fp32 word
     ptr = ws.data_ptr() + (-ws.data_ptr()) % 256
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     for name in names:
