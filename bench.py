@@ -143,6 +143,29 @@ HOST_PLAN = True           # --plan: the host passes the fragment lengths it kno
 STABLE_FRAGMENTS = 1       # --stable: the shared prompt (fragment 0) is not written during a decode step
 
 
+def parity_against_stored_reference(name: str, out: torch.Tensor):
+    """Layer 0 of every workload is the seeded problem itself: compare the output every rank ends up with against
+    the reference's own output for that problem (``tests/golden``; tolerance of the parity gate: max-abs <= 2e-2,
+    mean-abs <= 2e-3 for 16-bit outputs).  Returns None for length-scaled or otherwise unstored problems."""
+    import numpy as np
+    if LENGTH_SCALE != 1.0 or EMULATE_SHARD > 1:
+        return None
+    try:
+        if name == "cfg5":
+            ref = np.load(os.path.join(ROOT, "tests", "golden", "cfg5_g0_full.npz"))["out"]
+        else:
+            ref = np.load(os.path.join(ROOT, "tests", "golden", "reference_outputs.npz"))[f"{name}/out"]
+    except Exception:
+        return None
+    got = out.detach().float().cpu().numpy()
+    if got.shape != ref.shape:
+        return {"checked": True, "ok": False, "why": f"shape {got.shape} != {ref.shape}"}
+    diff = np.abs(got - ref)
+    mx, mean = float(diff.max()), float(diff.mean())
+    return {"checked": True, "ok": bool(np.isfinite(got).all() and mx <= 2e-2 and mean <= 2e-3), "max_abs": round(mx, 6),
+            "mean_abs": round(mean, 7), "against": "reference output stored in tests/golden (layer 0 of the step)"}
+
+
 class CabiCall:
     """One pre-bound C-ABI call (pointers fixed, so the step can be captured into a CUDA graph)."""
 
@@ -270,6 +293,20 @@ def run_ours(args):
             step_body(stream.cuda_stream)
             torch.cuda.synchronize()
             barrier()
+            # what this rank holds for layer 0 after one step (at N > 1: the gathered, full-size output)
+            if fused_gather:
+                first_out = peer_out.output(0)
+            elif dist:
+                first_out = gathered[0].permute(1, 0, 2, 3, 4).reshape(whole.W, whole.Hq, whole.S, whole.Ev)
+            else:
+                first_out = calls[0].out
+            parity = parity_against_stored_reference(workload, first_out)
+            if dist and parity is not None:          # every rank must hold the right answer
+                flag = torch.tensor([1 if parity["ok"] else 0], dtype=torch.int32, device=device)
+                worst = torch.tensor([parity.get("max_abs", 1e9)], dtype=torch.float64, device=device)
+                dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+                dist.all_reduce(worst, op=dist.ReduceOp.MAX)
+                parity.update(ok=bool(int(flag.item())), max_abs=round(float(worst.item()), 6), ranks_checked=world)
             # NCCL collectives stay outside graphs: capturing them stalled this benchmark on a 2-GPU box
             graph = None if (dist and not fused_gather) else capture(step_body)
 
@@ -316,7 +353,8 @@ def run_ours(args):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         res = dict(secs=float(t[0]), secs_attn=float(t[1]) or None, n_calls=steps * len(calls), bytes_per_call=bytes_per_call,
                    launches_per_step=launches_per_step, graph=graph is not None, fused_gather=fused_gather, iso_us=iso_us,
-                   clocks=clocks, full=full, layers=len(calls), kv_resident=int(sum(p.algorithmic_bytes() for p in probs)))
+                   clocks=clocks, full=full, layers=len(calls), kv_resident=int(sum(p.algorithmic_bytes() for p in probs)),
+                   parity=parity)
         del calls, probs, graph, gathered, peer_out, peer_tables
         torch.cuda.empty_cache()
         return res
@@ -343,7 +381,8 @@ def run_ours(args):
             e = {"us_per_call": round(t_call * 1e6, 3),
                  "value_TBps": round(x["bytes_per_call"] / t_call / 1e12, 4),
                  "attention_only_us_per_call": round(x["secs_attn"] / x["n_calls"] * 1e6, 3) if x["secs_attn"] else None,
-                 "layers_per_step": x["layers"], "steps": steps, "bytes_per_call": x["bytes_per_call"]}
+                 "layers_per_step": x["layers"], "steps": steps, "bytes_per_call": x["bytes_per_call"],
+                 "parity": x["parity"]}
             if name == "cfg5":
                 flops = wl.baseline_problem(name).flops()
                 e.update({"bound": "tensor", "flops_per_call": flops,
@@ -379,6 +418,7 @@ def run_ours(args):
         "us_per_call_isolated_cold": round(iso_us, 3),
         "pct_of_nominal_8TBps": round(100 * value * 1e3 / (NOMINAL_HBM_GBS * world), 2),
         "gpu_launches": launches_per_step * args.steps,
+        "parity_checked": bool(m["parity"] and m["parity"]["ok"]), "parity": m["parity"],
         "clocks": clocks,
         "e2e": e2e,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",

@@ -14,14 +14,18 @@
 //   * K, V and Q tiles are fetched by TMA (cp.async.bulk.tensor, one tensor map per fragment, encoded on the
 //     host) into shared memory in the 128-byte-swizzled layout the tensor core reads directly.
 //   * S = Q K^T (128 x 128 x 128) and O += P V (128 x 128 x 128) are tcgen05.mma instructions issued by one
-//     thread; S (two buffers) and O live in tensor memory.  Four softmax warps -- one thread per query row -- pull
-//     S out of tensor memory (tcgen05.ld), mask, exponentiate, write P as bf16/f16 into shared memory for the
-//     second MMA, and keep the running max and sum in registers.  O is rescaled in tensor memory only when a row's
+//     thread; S (two buffers) and O live in tensor memory.  The softmax warps pull S out of tensor memory
+//     (tcgen05.ld), mask, exponentiate, write P as bf16/f16 into shared memory for the second MMA, and keep the
+//     running max and sum in registers.  O is rescaled in tensor memory only when a row's
 //     max has grown by more than 2^8 since the scale it is stored at (then exp2 arguments stay below 8 and
 //     nothing overflows); the stored scale travels with the partial result, so the merge is exact.
 //
-// Warp roles (192 threads): warps 0-3 softmax (warp w owns tensor-memory lanes 32w..32w+31), warp 4 issues the
-// K/V copies, warp 5 allocates tensor memory, issues the Q copies and every MMA.  Every wait is bounded.
+// Warp roles (320 threads): warps 0-7 softmax, warp 8 issues the K/V copies, warp 9 allocates tensor memory, issues
+// the Q copies and every MMA.  Softmax warps w and w + 4 share the 32 query rows of tensor-memory lanes
+// 32 (w % 4) ... + 31 and split the 128 columns of S (keys) and of O between them: two warps per scheduler hide each
+// other's latencies, and a thread keeps 64 scores in registers.  Both derive the same row maximum -- each also
+// reads the other half's scores for that, which costs two more tensor-memory loads and no synchronisation -- so
+// the probabilities of a row share one scale.  Every wait is bounded.
 //
 // The reference has no counterpart: its kernel gives every (kv head, worker, token) its own CTAs and re-reads the
 // KV once per (worker, token) on CUDA cores (src/kernels/kernel_v21.cuh:62-66,957-964).
@@ -35,7 +39,11 @@ namespace hogatt {
 constexpr int kDenseMaxFragments = 16;      // tensor maps travel in the kernel arguments
 constexpr int kDenseRows = 128;             // query rows per CTA (MMA M)
 constexpr int kDenseTile = 128;             // keys per tile (MMA N of S, K of PV)
-constexpr int kDenseThreads = 192;
+// Softmax warps per 32-row group: each takes 128 / SPLIT columns of every row.  (Measured on the 1,024-row shape: two
+// beat four -- every warp re-reads the whole row for the maximum, so four warps issue 1.7 times the instructions.)
+constexpr int kDenseSplit = 2;
+constexpr int kDenseSoftmaxWarps = 4 * kDenseSplit;
+constexpr int kDenseThreads = (kDenseSoftmaxWarps + 2) * 32;
 
 struct alignas(64) DenseMaps {
     CUtensorMap q;                          // [F, W, Hkv, G*S, E] view of the rotated queries
@@ -53,12 +61,13 @@ struct DenseCfg {
     static constexpr int OFF_K = OFF_P + TILE_BYTES;
     static constexpr int OFF_V = OFF_K + NK * TILE_BYTES;
     static constexpr int OFF_BAR = OFF_V + NV * TILE_BYTES;                 // 224 KiB of tiles
-    // barriers: q_full, k_full[NK], k_empty[NK], v_full[NV], v_empty[NV], s_full[2], s_free[2], p_full, o_done
-    static constexpr int NBAR = 1 + 2 * NK + 2 * NV + 2 + 2 + 1 + 1;
+    // barriers: q_full, k_full[NK], k_empty[NK], v_full[NV], v_empty[NV], s_full[2], s_free[2], p_full, o_done, l_ready[4]
+    static constexpr int NBAR = 1 + 2 * NK + 2 * NV + 2 + 2 + 1 + 1 + 4;
     static constexpr int OFF_MISC = OFF_BAR + NBAR * 8;                     // tmem base, abort flag
     static constexpr int OFF_PLAN = OFF_MISC + 16;                          // vis[F], pre[F + 1]
     static constexpr int TMEM_COLS = 512;
     static constexpr int COL_O = 0, COL_S0 = 128, COL_S1 = 256;
+    static constexpr int COL_L = 384;           // 2 x 4 columns: the column groups' shares of the row sums, handed over at a flush
 };
 
 __host__ __device__ inline size_t dense_smem_bytes(int F) {
@@ -143,6 +152,27 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float (&v)[32]) 
           "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
         : "memory");
 }
+// 2^x, the hardware approximation (about two units in the last place); -inf gives 0
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ void tmem_st1(uint32_t taddr, float v) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "r"(__float_as_uint(v)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld4(uint32_t taddr, float (&v)[4]) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(v);
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(taddr)
+                 : "memory");
+}
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
@@ -197,13 +227,14 @@ dense_attention_kernel(const __grid_constant__ KernelArgs a, const __grid_consta
     const uint32_t bars = sbase + C::OFF_BAR;
     const uint32_t q_full = bars, k_full = q_full + 8, k_empty = k_full + 8 * C::NK, v_full = k_empty + 8 * C::NK,
                    v_empty = v_full + 8 * C::NV, s_full = v_empty + 8 * C::NV, s_free = s_full + 16, p_full = s_free + 16,
-                   o_done = p_full + 8;
+                   o_done = p_full + 8, l_ready = o_done + 8;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(base + C::OFF_MISC);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(base + C::OFF_MISC + 8);
     int* vis = reinterpret_cast<int*>(base + C::OFF_PLAN);
     int* pre = vis + a.F;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    HOGATT_TL_DECL;
 
     if (tid == 0) {
         mbar_init(q_full, 1);
@@ -217,15 +248,16 @@ dense_attention_kernel(const __grid_constant__ KernelArgs a, const __grid_consta
         }
         for (int s = 0; s < 2; ++s) {
             mbar_init(s_full + 8 * s, 1);
-            mbar_init(s_free + 8 * s, 4);      // one arrival per softmax warp
+            mbar_init(s_free + 8 * s, kDenseSoftmaxWarps);      // one arrival per softmax warp
         }
-        mbar_init(p_full, 4);
+        mbar_init(p_full, kDenseSoftmaxWarps);
         mbar_init(o_done, 1);
+        for (int s = 0; s < 4; ++s) mbar_init(l_ready + 8 * s, kDenseSplit - 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         fence_proxy_async_smem();
     }
-    if (warp == 5) tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
+    if (warp == kDenseSoftmaxWarps + 1) tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
     if (a.host_plan) {
         if (warp == 0) host_tile_prefix(a, kDenseTile, vis, pre);
         tc_fence_before();
@@ -252,7 +284,7 @@ dense_attention_kernel(const __grid_constant__ KernelArgs a, const __grid_consta
     }
     const int GS = a.G * a.S;
 
-    if (warp == 4) {
+    if (warp == kDenseSoftmaxWarps) {
         // ============================== K / V copies ==============================
         if (lane == 0) {
             DenseWalk walk(vis, pre, a.F, a.Hkv, t0, t1);
@@ -276,7 +308,7 @@ dense_attention_kernel(const __grid_constant__ KernelArgs a, const __grid_consta
                 tma_load_3d(vdst + C::ATOM_BYTES, &maps.v[d.f], 64, d.tok0, d.hkv, v_full + 8 * vs);
             }
         }
-    } else if (warp == 5) {
+    } else if (warp == kDenseSoftmaxWarps + 1) {
         // ============================== Q copies and every MMA ==============================
         if (lane == 0) {
             constexpr uint32_t IDESC_S = umma_idesc<T>(false, kDenseRows, kDenseTile);
@@ -329,6 +361,7 @@ dense_attention_kernel(const __grid_constant__ KernelArgs a, const __grid_consta
                     reload = nxt.new_segment;
                     if (!reload) {
                         ok = issue_s(it + 1);
+                        HOGATT_TL(0, 3000 + it);
                         if (!ok) break;
                     } else {
                         // the query tile changes: S_it must be finished with the old one before it is overwritten
@@ -338,6 +371,7 @@ dense_attention_kernel(const __grid_constant__ KernelArgs a, const __grid_consta
                         load_q(nxt);
                     }
                 }
+                HOGATT_TL(0, 1000 + it);
                 // O (+)= P_it V_it
                 const int vs = it % C::NV;
                 ok = mbar_wait_bounded(p_full, ((uint32_t)it) & 1u, abort_flag, a.status, STATUS_WAIT_SYNC_TIMEOUT) &&
@@ -354,6 +388,7 @@ dense_attention_kernel(const __grid_constant__ KernelArgs a, const __grid_consta
                 }
                 tc_commit(o_done);
                 tc_commit(v_empty + 8 * vs);
+                HOGATT_TL(0, 2000 + it);
                 if (reload) {
                     ok = mbar_wait_bounded(q_full, q_phase, abort_flag, a.status, STATUS_WAIT_FULL_TIMEOUT);
                     q_phase ^= 1u;
@@ -362,11 +397,20 @@ dense_attention_kernel(const __grid_constant__ KernelArgs a, const __grid_consta
             }
         }
     } else {
-        // ============================== softmax: one thread per query row ==============================
-        const int row = tid;                                   // row of the block == tensor-memory lane
-        const uint32_t lane_base = ((uint32_t)(warp * 32)) << 16;
-        const uint32_t p_row = sbase + C::OFF_P + row * 128;   // this row's 128 bytes inside a [128][64] swizzled atom
-        float m_run = -INFINITY, l_run = 0.f;
+        // ============================== softmax: SPLIT threads per query row, 128 / SPLIT columns each ==============================
+        constexpr int SPLIT = kDenseSplit, COLS = kDenseTile / SPLIT;      // COLS is 32 or 64
+        static_assert(COLS == 32 || COLS == 64, "a thread owns one or two 32-column tensor-memory loads");
+        const int row = (warp & 3) * 32 + lane;                // row of the block == tensor-memory lane
+        const int part = warp >> 2;                            // which COLS columns of S, P and O this thread owns
+        const int col0 = part * COLS;
+        const uint32_t lane_base = ((uint32_t)((warp & 3) * 32)) << 16;
+        // this thread's 2 * COLS bytes of P inside the row's 128 bytes of a [128][64] swizzled atom
+        const uint32_t p_row = sbase + C::OFF_P + (col0 >> 6) * C::ATOM_BYTES + row * 128;
+        const int p_chunk0 = (col0 & 63) >> 3;                 // first 16-byte chunk (before the swizzle)
+        const float scale2 = a.l2scale;                        // scores are raw dot products; exp2((s - m) * scale2)
+        const float grow_by = 8.f / scale2;                    // raw-score distance that equals a factor 2^8
+        float m_run = -INFINITY, l_run = 0.f;                  // running max (raw), this thread's share of the running sum
+        uint32_t nflush = 0;
         int lim = 0, vlen = 0;
         bool valid = false;
         RowId id = {0, 0, 0};
@@ -387,52 +431,82 @@ dense_attention_kernel(const __grid_constant__ KernelArgs a, const __grid_consta
                 lim = valid ? min(a.loc[(d.f * a.W + id.w) * a.S + id.s], vlen - 1) + 1 : vlen;
             }
             const int sb = it & 1;
+            if (warp == 0) HOGATT_TL(1, 1000 + it);
             ok = mbar_wait_bounded(s_full + 8 * sb, ((uint32_t)(it >> 1)) & 1u, abort_flag, a.status, STATUS_WAIT_FULL_TIMEOUT);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) break;
             tc_fence_after();
-            float s[128];
-            {
-                const uint32_t src = tmem + lane_base + (sb ? C::COL_S1 : C::COL_S0);
-#pragma unroll
-                for (int c = 0; c < 4; ++c) tmem_ld32(src + c * 32, *reinterpret_cast<float(*)[32]>(&s[c * 32]));
-                tmem_wait_ld();
-            }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(s_free + 8 * sb);        // the next S MMA may overwrite this buffer
-
-            // ---- scale, mask, tile max ----
+            if (warp == 0) HOGATT_TL(1, 2000 + it);
+            // ---- this thread's scores stay in registers; the other columns are only folded into the row maximum ----
+            const uint32_t src = tmem + lane_base + (sb ? C::COL_S1 : C::COL_S0);
             const int nvis = lim - d.tok0;                      // keys of this tile the row sees: [0, nvis)
-            float mx = -INFINITY;
-            if (nvis >= kDenseTile) {
+            float s[COLS];
+            float mx0 = -INFINITY, mx1 = -INFINITY;
+            {
+                // every load is issued before the first is waited for (one tensor-memory round trip per tile)
+                constexpr int NOTHER = (kDenseTile - COLS) / 32;
+                float other[NOTHER][32];
 #pragma unroll
-                for (int c = 0; c < 128; ++c) {
-                    s[c] *= a.l2scale;
-                    mx = fmaxf(mx, s[c]);
-                }
-            } else {
+                for (int c = 0; c < COLS / 32; ++c) tmem_ld32(src + col0 + c * 32, *reinterpret_cast<float(*)[32]>(&s[c * 32]));
 #pragma unroll
-                for (int c = 0; c < 128; ++c) {
-                    s[c] = c < nvis ? s[c] * a.l2scale : -INFINITY;
-                    mx = fmaxf(mx, s[c]);
+                for (int c = 0; c < NOTHER; ++c) tmem_ld32(src + ((col0 + COLS + c * 32) & (kDenseTile - 1)), other[c]);
+                tmem_wait_ld();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(s_free + 8 * sb);    // the next S MMA may overwrite this buffer
+                if (nvis >= kDenseTile) {
+#pragma unroll
+                    for (int c = 0; c < NOTHER; ++c)
+#pragma unroll
+                        for (int k = 0; k < 32; k += 4) {
+                            mx0 = max3(mx0, other[c][k], other[c][k + 1]);
+                            mx1 = max3(mx1, other[c][k + 2], other[c][k + 3]);
+                        }
+#pragma unroll
+                    for (int k = 0; k < COLS; k += 4) {
+                        mx0 = max3(mx0, s[k], s[k + 1]);
+                        mx1 = max3(mx1, s[k + 2], s[k + 3]);
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < NOTHER; ++c) {
+                        const int ob = (col0 + COLS + c * 32) & (kDenseTile - 1);
+#pragma unroll
+                        for (int k = 0; k < 32; ++k) mx0 = fmaxf(mx0, ob + k < nvis ? other[c][k] : -INFINITY);
+                    }
+#pragma unroll
+                    for (int k = 0; k < COLS; ++k) {
+                        s[k] = col0 + k < nvis ? s[k] : -INFINITY;
+                        mx1 = fmaxf(mx1, s[k]);
+                    }
                 }
             }
-            // O is stored at scale 2^-m_run.  It is only brought to a new scale when the row's max has grown by
-            // more than 8 (then every exponent below stays <= 8) or when nothing has been accumulated yet.
-            const bool grow = mx > m_run + 8.f || (m_run == -INFINITY && mx > -INFINITY);
+            if (warp == 0) HOGATT_TL(1, 3000 + it);
+            const float mx = fmaxf(mx0, mx1);
+            // O is stored at scale 2^(-m_run * scale2).  It is only brought to a new scale when the row's max has
+            // grown by more than a factor 2^8 (so every exponent below stays <= 8) or nothing has been accumulated yet.
+            const bool grow = mx > m_run + grow_by;                     // (m_run = -inf: any finite max grows it)
             const float m_new = grow ? mx : m_run;
             const float mu = (m_new == -INFINITY) ? 0.f : m_new;
-            const float alpha = grow ? exp2f(m_run - mu) : 1.f;     // (m_run = -inf -> 0)
+            const float alpha = grow ? fast_exp2((m_run - mu) * scale2) : 1.f;      // (m_run = -inf -> 0)
             m_run = m_new;
-            float sum = 0.f;
+            const float bias = -mu * scale2;
+            float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
+            uint32_t packed[COLS / 2];
 #pragma unroll
-            for (int c = 0; c < 128; ++c) {
-                s[c] = exp2f(s[c] - mu);
-                sum += s[c];
+            for (int c = 0; c < COLS; c += 4) {
+                const float e0 = fast_exp2(fmaf(s[c], scale2, bias)), e1 = fast_exp2(fmaf(s[c + 1], scale2, bias));
+                const float e2 = fast_exp2(fmaf(s[c + 2], scale2, bias)), e3 = fast_exp2(fmaf(s[c + 3], scale2, bias));
+                sum0 += e0;
+                sum1 += e1;
+                sum2 += e2;
+                sum3 += e3;
+                packed[c / 2] = pack2<T>(e0, e1);
+                packed[c / 2 + 1] = pack2<T>(e2, e3);
             }
-            l_run = l_run * alpha + sum;
+            l_run = l_run * alpha + ((sum0 + sum1) + (sum2 + sum3));
 
+            if (warp == 0) HOGATT_TL(1, 4000 + it);
             // ---- P and O become writable once the previous tile's second MMA has finished ----
             if (it > 0) {
                 ok = mbar_wait_bounded(o_done, ((uint32_t)(it - 1)) & 1u, abort_flag, a.status, STATUS_WAIT_SYNC_TIMEOUT);
@@ -441,9 +515,9 @@ dense_attention_kernel(const __grid_constant__ KernelArgs a, const __grid_consta
                 tc_fence_after();
             }
             if (!d.first_of_unit && __any_sync(0xffffffffu, grow)) {
-                const uint32_t o_addr = tmem + lane_base + C::COL_O;
+                const uint32_t o_addr = tmem + lane_base + C::COL_O + col0;
 #pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
+                for (int c = 0; c < COLS / 32; ++c) {
                     float o[32];
                     tmem_ld32(o_addr + c * 32, o);
                     tmem_wait_ld();
@@ -453,36 +527,34 @@ dense_attention_kernel(const __grid_constant__ KernelArgs a, const __grid_consta
                 }
                 tmem_wait_st();
             }
+            if (warp == 0) HOGATT_TL(1, 5000 + it);
             // ---- P (storage type) into shared memory, 128-byte swizzle: 16-byte chunk c of row r sits at c ^ (r & 7) ----
 #pragma unroll
-            for (int c = 0; c < 16; ++c) {
-                uint4 v;
-                v.x = pack2<T>(s[c * 8 + 0], s[c * 8 + 1]);
-                v.y = pack2<T>(s[c * 8 + 2], s[c * 8 + 3]);
-                v.z = pack2<T>(s[c * 8 + 4], s[c * 8 + 5]);
-                v.w = pack2<T>(s[c * 8 + 6], s[c * 8 + 7]);
-                const uint32_t dst = p_row + (c >> 3) * C::ATOM_BYTES + (((c & 7) ^ (row & 7)) << 4);
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+            for (int c = 0; c < COLS / 8; ++c) {
+                const uint32_t dst = p_row + (((p_chunk0 + c) ^ (row & 7)) << 4);
+                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(packed[4 * c]), "r"(packed[4 * c + 1]),
+                             "r"(packed[4 * c + 2]), "r"(packed[4 * c + 3])
+                             : "memory");
             }
             // V rows at or past the fragment's true length may hold anything (spare rows of a slab, fetched as they
-            // are): their probabilities are exactly zero, but 0 * NaN would poison O.  Zero them in the staged tile.
+            // are): their probabilities are exactly zero, but 0 * NaN would poison O.  Zero them in the staged tile
+            // (each thread its share of the row's bytes).
             if (d.tok0 + kDenseTile > vlen) {
                 const int vs = it % C::NV;
                 ok = mbar_wait_bounded(v_full + 8 * vs, ((uint32_t)(it / C::NV)) & 1u, abort_flag, a.status, STATUS_WAIT_FULL_TIMEOUT);
                 ok = __all_sync(0xffffffffu, ok);
                 if (!ok) break;
                 if (d.tok0 + row >= vlen) {
-                    unsigned char* vrow = base + C::OFF_V + vs * C::TILE_BYTES + row * 128;
+                    unsigned char* vrow = base + C::OFF_V + vs * C::TILE_BYTES + (col0 >> 6) * C::ATOM_BYTES + row * 128 + (col0 & 63) * 2;
 #pragma unroll
-                    for (int h = 0; h < 2; ++h)
-#pragma unroll
-                        for (int c = 0; c < 8; ++c) *reinterpret_cast<int4*>(vrow + h * C::ATOM_BYTES + c * 16) = make_int4(0, 0, 0, 0);
+                    for (int c = 0; c < COLS / 8; ++c) *reinterpret_cast<int4*>(vrow + c * 16) = make_int4(0, 0, 0, 0);
                 }
             }
             fence_proxy_async_smem();          // generic-proxy writes (P, V rows) before the MMA's async-proxy reads
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full);
+            if (warp == 0) HOGATT_TL(1, 6000 + it);
 
             // ---- end of this CTA's share of the unit: leave the partial result ----
             if (d.last_of_unit) {
@@ -493,10 +565,10 @@ dense_attention_kernel(const __grid_constant__ KernelArgs a, const __grid_consta
                 int first, count;
                 unit_ctas(d.u, TH, N, ctas, &first, &count);
                 const size_t slot = (size_t)d.u * a.parts_per_unit + (blockIdx.x - first);
-                float* wo = a.ws_o + (slot * kDenseRows + row) * C::HD;
-                const uint32_t o_addr = tmem + lane_base + C::COL_O;
+                float* wo = a.ws_o + (slot * kDenseRows + row) * C::HD + col0;
+                const uint32_t o_addr = tmem + lane_base + C::COL_O + col0;
 #pragma unroll 1
-                for (int c = 0; c < 4; ++c) {
+                for (int c = 0; c < COLS / 32; ++c) {
                     float o[32];
                     tmem_ld32(o_addr + c * 32, o);
                     tmem_wait_ld();
@@ -504,8 +576,30 @@ dense_attention_kernel(const __grid_constant__ KernelArgs a, const __grid_consta
                     for (int k = 0; k < 8; ++k)
                         *reinterpret_cast<float4*>(wo + c * 32 + k * 4) = make_float4(o[4 * k], o[4 * k + 1], o[4 * k + 2], o[4 * k + 3]);
                 }
-                a.ws_m[slot * kDenseRows + row] = m_run;
-                a.ws_l[slot * kDenseRows + row] = l_run;
+                // The row's sum is the column groups' shares added up.  Groups 1.. hand theirs to group 0 through four
+                // spare tensor-memory columns (two sets, alternating: group 0 may still be reading the previous set).
+                const uint32_t l_addr = tmem + lane_base + C::COL_L + (nflush & 1u) * 4;
+                if (part != 0) {
+                    tmem_st1(l_addr + part, l_run);
+                    tmem_wait_st();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(l_ready + 8 * (warp & 3));
+                } else {
+                    ok = mbar_wait_bounded(l_ready + 8 * (warp & 3), nflush & 1u, abort_flag, a.status, STATUS_WAIT_SYNC_TIMEOUT);
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
+                    tc_fence_after();
+                    float shares[4];
+                    tmem_ld4(l_addr, shares);
+                    tmem_wait_ld();
+                    float total = l_run;
+#pragma unroll
+                    for (int k = 1; k < SPLIT; ++k) total += shares[k];
+                    a.ws_m[slot * kDenseRows + row] = m_run == -INFINITY ? -INFINITY : m_run * scale2;
+                    a.ws_l[slot * kDenseRows + row] = total;
+                }
+                ++nflush;
                 tc_fence_before();
             }
         }
@@ -514,7 +608,7 @@ dense_attention_kernel(const __grid_constant__ KernelArgs a, const __grid_consta
     // ---- common exit: nobody leaves before tensor memory can be handed back ----
     tc_fence_before();
     __syncthreads();
-    if (warp == 5) {
+    if (warp == kDenseSoftmaxWarps + 1) {
         tc_fence_after();
         tmem_dealloc(tmem, C::TMEM_COLS);
     }
