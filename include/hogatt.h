@@ -68,11 +68,11 @@ typedef enum hogatt_status {
  * launch shapes: a persistent grid (one CTA per SM over balanced tile ranges, partial results in the
  * workspace, a merge kernel after it) and a thread-block-cluster grid (one cluster per kv head and row
  * block, partial results merged through distributed shared memory inside the same kernel, nothing
- * written to the workspace).  AUTO takes the cluster shape when few units are left on the GPU (kv heads
- * sharded over GPUs: each unit would leave 37-148 partials for the merge kernel) and the call is short
- * enough for units x 16 SMs to stream it, and the persistent grid otherwise; MMA forces the persistent
- * grid, MMA_CLUSTER forces the cluster shape (HOGATT_ERR_BAD_KERNEL_CHOICE when there are more units than half the SMs, or the device cannot
- * hold one cluster per unit at once).  hogatt_launch_shape() tells which one a problem gets.
+ * written to the workspace).  AUTO and MMA take the persistent grid (on B200 it is the faster one at every
+ * measured shape, its merge step folding any number of partials per row in one memory round trip);
+ * MMA_CLUSTER forces the cluster shape (HOGATT_ERR_BAD_KERNEL_CHOICE when there are more units than half
+ * the SMs, or the device cannot hold one cluster per unit at once).  hogatt_launch_shape() tells which one
+ * a problem gets.
  *
  * DENSE is the kernel for calls with many query rows per kv head (W x Hq/Hkv x S >= 128, e.g. workers that
  * each issue a 16-token chunk), where the op is bound by the tensor pipe, not by HBM: 128-row query blocks,
@@ -222,11 +222,12 @@ int hogatt_fused_launch_static(const hogatt_problem* p, hogatt_stream_t stream);
  * ignored) and a table of peer-mapped pointers.  The merge step stores each finished output row straight
  * into the full-size output [W, world*Hq, S, Ev] of EVERY rank (plain stores over NVLink through the peer
  * mapping) at this rank's head offset; a one-warp kernel then publishes a per-call count to every peer
- * and waits, for at most about a second (then: bit 32 in device_status), until all peers have published
- * theirs.  When the call's work has completed on a rank's stream, that rank's out_full is complete.
+ * (release at system scope) and waits, for at most about a second (then: bit 32 in device_status;
+ * HOGATT_WAIT_LIMIT_MS in the environment shortens it), until all peers have published theirs.  When the
+ * call's work has completed on a rank's stream, that rank's out_full is complete.
  *   out_full[p], flags[p]: rank p's buffers as mapped into THIS GPU's address space (CUDA IPC / VMM /
  *       symmetric memory); flags[p] is int32[world + 1], zero-filled once before the first call
- *       (slot world is rank p's own call counter).
+ *       (slots 0 .. world-1: the counts the ranks publish; slot world: rank p's own call counter).
  *   The caller must not let a rank start call k+1 on an out_full that another rank is still reading
  *   from call k (alternate two buffers, or synchronise the consumers).
  */

@@ -49,6 +49,10 @@ int current_device_info(int* dev, int* sms, int* smem_optin) {
         int s = 0, m = 0;
         HOGATT_CUDA_OK(cudaDeviceGetAttribute(&s, cudaDevAttrMultiProcessorCount, *dev));
         HOGATT_CUDA_OK(cudaDeviceGetAttribute(&m, cudaDevAttrMaxSharedMemoryPerBlockOptin, *dev));
+        if (const char* ms = getenv("HOGATT_WAIT_LIMIT_MS")) {      // tests of the give-up path shorten every bounded wait
+            const unsigned long long ns = (unsigned long long)std::max(1, atoi(ms)) * 1000000ull;
+            HOGATT_CUDA_OK(cudaMemcpyToSymbol(g_wait_limit_ns, &ns, sizeof(ns)));
+        }
         d.smem_optin.store(m, std::memory_order_release);
         d.sms.store(s, std::memory_order_release);
         n = s;
@@ -330,31 +334,19 @@ int mma_best_cluster_dims(int HD, int MT, int dev, int F, int smem_optin, int un
 }
 
 // CTAs per cluster if this problem runs as the self-merging cluster variant on the current device, else 0
-// (persistent grid + merge kernel).  The cluster variant saves the partials' trip through the workspace
-// and the second launch, but it only uses units * cluster SMs and one SM pulls about 66 GB/s.  Measured on
-// B200 (us per call, B bytes streamed, n CTAs, p = SMs / units partials per unit for the merge kernel):
-//   persistent grid ~ 8.9 + 0.12 * p + B / 6.5 TB/s        cluster ~ 9.0 + B / (min(n, 64) * 66 GB/s)
-// With 8 kv heads on the GPU (p = 18.5) the persistent grid wins at every context length (10.4 / 12.9 / 16.2 /
-// 20.6 us at 2K / 4K / 8K / 16K keys against 13.3 / 14.6 / 17.7 / 22.4); the cluster shape wins when the kv
-// heads are sharded over GPUs and few units are left per GPU, because then every unit has 37-148 partials to
-// merge: north-star shape at 2 / 4 / 8 GPUs 17.0 / 16.6 / 16.5 us against 18.6 / 20.6 / 23.4.
-constexpr double kPersistFixedUs = 8.9, kPersistPerPartUs = 0.12, kClusterFixedUs = 9.0, kChipBytesPerUs = 6.5e6,
-                 kSmBytesPerUs = 66e3;
-constexpr int kClusterUsefulCtas = 64;
-constexpr int kClusterMinPartsPerUnit = 30;      // below that many partials per unit the merge kernel is cheap enough
+// (persistent grid + merge kernel).  The cluster variant saves the partials' trip through the workspace and the
+// second launch, but it only uses units * cluster SMs (at most 16 per unit, and only as many clusters as are resident
+// at once), and one SM pulls about 66 GB/s.  Measured on B200 it loses to the persistent grid everywhere since the
+// merge step handles many partials per row in one round trip (one rank's share of an 8-way kv-head split: 16,384
+// keys 8.9 us against 14.8, 139,264 keys 20.7 us against 79), so AUTO never takes it; it runs on request only
+// (HOGATT_KERNEL_MMA_CLUSTER).
 int choose_cluster(const hogatt_problem* p, const Resolved& r, int dev, int sms, int smem_optin, int64_t tiles_per_unit) {
-    if (r.kernel != HOGATT_KERNEL_MMA || r.cluster_mode < 0 || 2 * r.units > sms) return 0;
+    (void)tiles_per_unit;
+    if (r.kernel != HOGATT_KERNEL_MMA || r.cluster_mode <= 0 || 2 * r.units > sms) return 0;
     int cs = 0;
     if (p->dtype == HOGATT_F16) cs = mma_best_cluster_dims<__half>(p->E, r.mt, dev, p->F, smem_optin, r.units, sms);
     if (p->dtype == HOGATT_BF16) cs = mma_best_cluster_dims<__nv_bfloat16>(p->E, r.mt, dev, p->F, smem_optin, r.units, sms);
-    if (cs == 0 || r.cluster_mode > 0) return cs;
-    if (p->max_ctas > 0) return 0;                       // the caller is testing grid sizes of the persistent variant
-    if (sms / r.units < kClusterMinPartsPerUnit) return 0;
-    cs = std::min(cs, std::max(2, kClusterUsefulCtas / r.units));
-    const double bytes = (double)tiles_per_unit * r.units * MmaCfg<128, 1>::STAGE_BYTES;
-    const double persistent = kPersistFixedUs + kPersistPerPartUs * sms / r.units + bytes / kChipBytesPerUs;
-    const double cluster = kClusterFixedUs + bytes / (kSmBytesPerUs * std::min(r.units * cs, kClusterUsefulCtas));
-    return cluster < persistent ? cs : 0;
+    return cs;
 }
 
 // cluster == 0: persistent grid of `grid` CTAs (merge_kernel must follow).
@@ -428,6 +420,25 @@ int launch_fma_dims(const KernelArgs& args, int dev, int smem_optin, int grid, c
         case 256: return launch_fma<T, 256>(args, dev, smem_optin, grid, stream);
     }
     return HOGATT_ERR_UNSUPPORTED_HEAD_DIM;
+}
+
+// The merge step after a persistent-grid attention kernel.  Up to 32 partial slots per unit: one warp per output row
+// (lean instantiation; 8 kv heads on one GPU leave 19-20 partials per row).  More -- kv heads sharded over GPUs, one
+// unit cut into 37 ... 148 partials -- one CTA per row whose eight warps share the partials (one memory round trip
+// instead of one per 24 partials), as long as that grid stays small; otherwise the batched one-warp-per-row kernel.
+template <class T>
+int launch_merge(const KernelArgs& args, const Resolved& r, cudaStream_t stream) {
+    if (args.parts_per_unit > 32 && (int64_t)r.units * r.rows_per_block <= 4096 && !(tune_flags() & 2)) {
+        dim3 wgrid((unsigned)r.units, (unsigned)r.rows_per_block);
+        HOGATT_CUDA_OK(launch_kernel(merge_wide_kernel<T>, wgrid, dim3(kWideWarps * 32), 0, stream, args));
+        return HOGATT_OK;
+    }
+    dim3 mgrid((unsigned)r.units, (unsigned)ceil_div(r.rows_per_block, kMergeWarps));
+    if (args.parts_per_unit <= 32)
+        HOGATT_CUDA_OK(launch_kernel(merge_kernel<T, 1>, mgrid, dim3(kMergeWarps * 32), 0, stream, args));
+    else
+        HOGATT_CUDA_OK(launch_kernel(merge_kernel<T, 5>, mgrid, dim3(kMergeWarps * 32), 0, stream, args));
+    return HOGATT_OK;
 }
 
 // ---- tcgen05 kernel: tensor maps and launch ------------------------------------------------------------------
@@ -555,12 +566,7 @@ int launch_all(const KernelArgs& args, const Resolved& r, int dev, int smem_opti
 #ifdef HOGATT_EXPERIMENT
     if (getenv("HOGATT_SKIP_MERGE")) return HOGATT_OK;
 #endif
-    dim3 mgrid((unsigned)r.units, (unsigned)ceil_div(r.rows_per_block, kMergeWarps));
-    if (args.parts_per_unit <= 32)
-        HOGATT_CUDA_OK(launch_kernel(merge_kernel<T, 1>, mgrid, dim3(kMergeWarps * 32), 0, stream, args));
-    else
-        HOGATT_CUDA_OK(launch_kernel(merge_kernel<T, 5>, mgrid, dim3(kMergeWarps * 32), 0, stream, args));
-    return HOGATT_OK;
+    return launch_merge<T>(args, r, stream);
 }
 
 template <>
@@ -568,12 +574,7 @@ int launch_all<float>(const KernelArgs& args, const Resolved& r, int dev, int sm
                       const void*) {
     int rc = launch_fma_dims<float>(args, dev, smem_optin, grid, stream);
     if (rc != HOGATT_OK) return rc;
-    dim3 mgrid((unsigned)r.units, (unsigned)ceil_div(r.rows_per_block, kMergeWarps));
-    if (args.parts_per_unit <= 32)
-        HOGATT_CUDA_OK(launch_kernel(merge_kernel<float, 1>, mgrid, dim3(kMergeWarps * 32), 0, stream, args));
-    else
-        HOGATT_CUDA_OK(launch_kernel(merge_kernel<float, 5>, mgrid, dim3(kMergeWarps * 32), 0, stream, args));
-    return HOGATT_OK;
+    return launch_merge<float>(args, r, stream);
 }
 
 bool aligned16(const void* p) { return ((uintptr_t)p & 15u) == 0; }
@@ -711,8 +712,8 @@ int attention_launch(const hogatt_problem* p, bool fused, cudaStream_t stream, c
     PeerFlags pf;
     memset(&pf, 0, sizeof(pf));
     for (int i = 0; i < peers->world; ++i) pf.f[i] = peers->flags[i];
-    gather_signal_kernel<<<1, 32, 0, stream>>>(pf, peers->world, peers->rank, p->device_status);
-    HOGATT_CUDA_OK(cudaGetLastError());
+    HOGATT_CUDA_OK(launch_kernel(gather_signal_kernel, dim3(1), dim3(32), 0, stream, pf, (int)peers->world, (int)peers->rank,
+                                 p->device_status));
     return HOGATT_OK;
 }
 

@@ -183,6 +183,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // records `bit` in the caller's status word, raises the CTA-wide abort flag and reports failure,
 // and every loop that sees a failed wait or the flag leaves without touching the tile.
 constexpr uint64_t kWaitLimitNs = 1000ull * 1000ull * 1000ull;
+// The limit the kernels read (only on the slow path of a wait): one second unless the host was started with
+// HOGATT_WAIT_LIMIT_MS in the environment, which the library copies here once per device (tests of the give-up path).
+__device__ unsigned long long g_wait_limit_ns = kWaitLimitNs;
 
 // The polling loop lives out of line: these kernels run for microseconds and their instruction fetch
 // shows in the call time, so every wait site is just a try_wait and a call.
@@ -198,7 +201,7 @@ __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volat
     while (!mbar_try_wait(bar, parity)) {
         if ((++spins & 63u) == 0) {
             if (*abort_flag) return false;
-            if (global_timer_ns() - t0 > kWaitLimitNs) {
+            if (global_timer_ns() - t0 > g_wait_limit_ns) {
                 *abort_flag = 1;
                 if (status) atomicOr(status, bit);
                 return false;

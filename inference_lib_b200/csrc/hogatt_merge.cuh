@@ -178,12 +178,148 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const __grid_co
 #endif
 }
 
+// Split-K merge for rows with MANY partials (kv heads sharded over GPUs: one unit cut into a partial per SM).  One CTA
+// per output row, eight warps; warp w folds partials w, w + 8, ... exactly like merge_partials_rows does (its own
+// maximum, denominator and weighted sum: one memory round trip for up to 192 partials per row), the eight results are
+// combined through shared memory.  The one-warp-per-row kernel above needs a round trip per 24 partials.
+constexpr int kWideWarps = 8;
+template <class T>
+__global__ void __launch_bounds__(kWideWarps * 32) merge_wide_kernel(const __grid_constant__ KernelArgs a) {
+    __shared__ float sm_m[kWideWarps], sm_l[kWideWarps];
+    __shared__ float4 sm_o[kWideWarps][64];               // up to 256 output columns
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int u = blockIdx.x, row = blockIdx.y;
+    const int rb = u / a.Hkv, hkv = u % a.Hkv;
+    if (!(a.tune & 1)) pdl_trigger();
+    pdl_wait();
+    if (a.tune & 1) pdl_trigger();
+    const int units = a.row_blocks * a.Hkv;
+    const int RPB = a.rows_per_block, Ev = a.Ev;
+    const int gr = rb * RPB + row;
+    if (gr >= a.rows_total) return;      // (uniform over the CTA)
+    int count = 0;
+    {
+        const int TH = a.host_plan ? a.plan_tiles : __ldcg(a.header), ctas = a.host_plan ? a.plan_ctas : __ldcg(a.header + 1);
+        int first = 0;
+        if (TH > 0) unit_ctas(u, TH, (int64_t)units * TH, ctas, &first, &count);
+    }
+    const size_t slot0 = (size_t)u * a.parts_per_unit;
+    constexpr int kPer = 24;                               // partials per warp per pass
+    float M = -INFINITY, L = 0.f;
+    float4 acc[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};     // columns lane*4 (+128)
+#pragma unroll 1
+    for (int p0 = warp; p0 < count; p0 += kWideWarps * kPer) {
+        // this pass: partials p0, p0 + 8, ...; lane k holds the statistics of the k-th of them
+        const int mine = p0 + lane * kWideWarps;
+        const bool have = lane < kPer && mine < count;
+        const float mp = have ? __ldcg(a.ws_m + (slot0 + mine) * RPB + row) : -INFINITY;
+        const float lp = have ? __ldcg(a.ws_l + (slot0 + mine) * RPB + row) : 0.f;
+        float4 x[kPer];
+        const bool wide = Ev > 128;
+#pragma unroll
+        for (int k = 0; k < kPer; ++k) {
+            const int p = min(p0 + k * kWideWarps, count - 1);
+            x[k] = lane * 4 < Ev ? __ldcg(reinterpret_cast<const float4*>(a.ws_o + ((slot0 + p) * RPB + row) * Ev + lane * 4))
+                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        float Mp = mp;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) Mp = fmaxf(Mp, __shfl_xor_sync(0xffffffffu, Mp, o));
+        const float Mn = fmaxf(M, Mp);
+        const float mu = Mn == -INFINITY ? 0.f : Mn;
+        const float rescale = exp2f(M - mu);               // (M = -inf -> 0)
+        const float w = have ? exp2f(mp - mu) : 0.f;
+        float den = lp * w;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
+        L = L * rescale + den;
+        M = Mn;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            acc[h].x *= rescale;
+            acc[h].y *= rescale;
+            acc[h].z *= rescale;
+            acc[h].w *= rescale;
+        }
+#pragma unroll
+        for (int k = 0; k < kPer; ++k) {
+            const float wk = __shfl_sync(0xffffffffu, w, k);
+            const bool used = p0 + k * kWideWarps < count;   // a repeated last slot must not count twice
+            acc[0].x = fmaf(used ? x[k].x : 0.f, wk, acc[0].x);
+            acc[0].y = fmaf(used ? x[k].y : 0.f, wk, acc[0].y);
+            acc[0].z = fmaf(used ? x[k].z : 0.f, wk, acc[0].z);
+            acc[0].w = fmaf(used ? x[k].w : 0.f, wk, acc[0].w);
+        }
+        if (wide) {                                         // columns 128 .. 255: a second pass over the same partials
+#pragma unroll 1
+            for (int k = 0; k < kPer; ++k) {
+                const int p = p0 + k * kWideWarps;
+                if (p >= count) break;
+                const float wk = __shfl_sync(0xffffffffu, w, k);
+                if (128 + lane * 4 < Ev) {
+                    const float4 y = __ldcg(reinterpret_cast<const float4*>(a.ws_o + ((slot0 + p) * RPB + row) * Ev + 128 + lane * 4));
+                    acc[1].x = fmaf(y.x, wk, acc[1].x);
+                    acc[1].y = fmaf(y.y, wk, acc[1].y);
+                    acc[1].z = fmaf(y.z, wk, acc[1].z);
+                    acc[1].w = fmaf(y.w, wk, acc[1].w);
+                }
+            }
+        }
+    }
+    if (lane == 0) {
+        sm_m[warp] = M;
+        sm_l[warp] = L;
+    }
+    sm_o[warp][lane] = acc[0];
+    sm_o[warp][32 + lane] = acc[1];
+    __syncthreads();
+    // every thread of the first two warps finishes four output columns
+    if (warp < 2 && (warp * 128 + lane * 4) < Ev) {
+        float Mx = sm_m[0];
+#pragma unroll
+        for (int k = 1; k < kWideWarps; ++k) Mx = fmaxf(Mx, sm_m[k]);
+        const float mu = Mx == -INFINITY ? 0.f : Mx;
+        float den = 0.f;
+        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int k = 0; k < kWideWarps; ++k) {
+            const float f = sm_m[k] == -INFINITY ? 0.f : exp2f(sm_m[k] - mu);      // a warp without partials holds zeros
+            const float4 y = sm_o[k][warp * 32 + lane];
+            den = fmaf(sm_l[k], f, den);
+            sum.x = fmaf(y.x, f, sum.x);
+            sum.y = fmaf(y.y, f, sum.y);
+            sum.z = fmaf(y.z, f, sum.z);
+            sum.w = fmaf(y.w, f, sum.w);
+        }
+        const float inv = den > 0.f ? 1.f / den : 0.f;
+        if (!(den > 0.f)) sum = make_float4(0.f, 0.f, 0.f, 0.f);
+        const RowId id = decode_row(gr, a.G, a.S);
+        T* const local_out = static_cast<T*>(a.out);
+        const int nbases = a.world > 0 ? a.world : 1;
+        const int hq_all = a.world > 0 ? a.world * a.Hq : a.Hq, hq_off = a.world > 0 ? a.rank * a.Hq : 0;
+        const size_t offset = ((size_t)(id.w * hq_all + hq_off + hkv * a.G + id.g) * a.S + id.s) * Ev + warp * 128 + lane * 4;
+        const T r0 = Scalar<T>::from_float(sum.x * inv), r1 = Scalar<T>::from_float(sum.y * inv);
+        const T r2 = Scalar<T>::from_float(sum.z * inv), r3 = Scalar<T>::from_float(sum.w * inv);
+        for (int b = 0; b < nbases; ++b) {
+            T* dst = (a.world > 0 ? static_cast<T*>(a.peer_out[b]) : local_out) + offset;
+            dst[0] = r0;
+            dst[1] = r1;
+            dst[2] = r2;
+            dst[3] = r3;
+        }
+    }
+}
+
 // Completion exchange of the fused output all-gather: one warp, lane p talks to rank p.
 //   1. bump this rank's call counter (device memory, so that a replayed CUDA graph still counts);
 //   2. publish the new count into slot `rank` of every peer's flag array (system-scope release: the
 //      merge kernel's peer stores, finished at the kernel boundary before this one, are visible first);
 //   3. wait -- bounded -- until every peer has published at least the same count into OUR flag array.
 // flags layout on every rank: int32[world] flags + int32 counter at index `world`.
+// (Publishing from the tail of the kernel that stores the rows instead -- every CTA fences its peer stores at
+// system scope and takes a ticket, the last one publishes, this kernel only waits -- was measured on two GPUs:
+// 29.7 ... 32.8 us per call against 21 ... 23 with the exchange behind the kernel boundary; the per-CTA
+// system-scope fences sit on the storing kernel's critical path.)
 struct PeerFlags {
     int* f[HOGATT_MAX_PEERS];
 };
@@ -192,6 +328,8 @@ __global__ void __launch_bounds__(32) gather_signal_kernel(const __grid_constant
     const int lane = threadIdx.x;
     int* mine = flags.f[rank];
     int epoch = 0;
+    pdl_trigger();       // the next call's attention kernel may be scheduled (it waits for this grid before it reads or writes anything of this call's)
+    pdl_wait();          // the rows are out: the storing kernel has completed and its stores are flushed
     if (lane == 0) epoch = atomicAdd(mine + world, 1) + 1;
     epoch = __shfl_sync(0xffffffffu, epoch, 0);
     if (lane < world) {
@@ -202,7 +340,7 @@ __global__ void __launch_bounds__(32) gather_signal_kernel(const __grid_constant
             int seen;
             asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(mine + lane) : "memory");
             if (seen >= epoch) break;
-            if (global_timer_ns() - t0 > kWaitLimitNs) {
+            if (global_timer_ns() - t0 > g_wait_limit_ns) {
                 if (status) atomicOr(status, STATUS_WAIT_PEER_TIMEOUT);
                 break;
             }

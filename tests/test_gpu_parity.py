@@ -87,14 +87,15 @@ def test_launch_shape_matches_what_runs():
     shape = _cabi.launch_shape(mk(_cabi.KERNEL_MMA_CLUSTER))
     assert shape["kernel"] == _cabi.KERNEL_MMA_CLUSTER and shape["kernels_per_call"] == 1
     assert 2 <= shape["cluster"] <= 16 and shape["ctas"] == 8 * shape["cluster"] <= sms
-    # left to itself the library takes the persistent grid for this shape (67 MB of K/V) ...
+    # left to itself the library takes the persistent grid for this shape ...
     assert _cabi.launch_shape(mk(_cabi.KERNEL_AUTO))["kernels_per_call"] == 2
-    # ... and clusters for one rank's share of the same shape when the kv heads are spread over 4 GPUs
+    # ... and for one rank's share of it when the kv heads are spread over 4 GPUs (clusters only on request)
     part = p.shard(0, 4).to("cuda:0")
     out4 = torch.empty((part.W, part.Hq, part.S, part.Ev), dtype=p.dtype, device="cuda:0")
-    bp = _cabi.bind(out=out4, queries=part.queries, locations=part.locations, keys=part.keys, values=part.values,
-                    scale=part.scale, cos=part.cos, sin=part.sin)
-    shape = _cabi.launch_shape(bp)
+    mk4 = lambda k: _cabi.bind(out=out4, queries=part.queries, locations=part.locations, keys=part.keys, values=part.values,
+                               scale=part.scale, cos=part.cos, sin=part.sin, kernel=k)
+    assert _cabi.launch_shape(mk4(_cabi.KERNEL_AUTO)) == dict(kernel=_cabi.KERNEL_MMA, ctas=sms, cluster=0, kernels_per_call=2)
+    shape = _cabi.launch_shape(mk4(_cabi.KERNEL_MMA_CLUSTER))
     assert shape["kernel"] == _cabi.KERNEL_MMA_CLUSTER and shape["cluster"] == 16 and shape["ctas"] == 32
 
 
