@@ -372,7 +372,7 @@ def run_ours(args):
         tf_peak, _ = measured_peak("bf16_tflops_sustained", FALLBACK_BF16_TFLOPS_SUSTAINED)
         extra = {}
         for name, layers, steps, warm in (("cfg2", 32, 100, 10), ("cfg3", 32, 100, 10), ("target", 32, 100, 10),
-                                          ("cfg4", 4, 30, 5), ("cfg5", 4, 10, 3)):
+                                          ("cfg4", 4, 30, 5), ("cfg5", 4, 10, 3), ("gqa16", 32, 100, 10)):
             if name == args.workload or (world > 1 and wl.BASELINE_CONFIGS[name]["Hkv"] % world):
                 continue
             x = measure(name, layers, steps, warm, False)
@@ -390,6 +390,9 @@ def run_ours(args):
                           "frac": round(flops / world / t_kernel / 1e12 / tf_peak, 4), "peak_TFLOPs": tf_peak})
             else:
                 e.update({"bound": "hbm", "frac": round(x["bytes_per_call"] / world / t_kernel / 1e9 / hbm_peak, 4)})
+            if name == "gqa16" and world == 1:
+                # the one head layout the reference's own CUDA kernel accepts: race it on the same GPU, same inputs
+                e["reference_cuda_kernel"] = race_reference_kernel(name, layers)
             extra[name] = e
     us_per_call = secs / n_calls * 1e6
     value = bytes_per_call * n_calls / secs / 1e12
@@ -515,6 +518,23 @@ def measure_e2e(args, p: wl.Problem, device, dist, world):
 # ------------------------------------------------------------------------------------------------
 # CPU legs (the only places that run the oracle)
 # ------------------------------------------------------------------------------------------------
+def race_reference_kernel(workload: str, layers: int):
+    """Time the reference's own CUDA kernels (``oracle/_ref/hogatt_ref.so``: ``kernel_v21`` recompiled for sm_100a) on
+    the same workload in a process of their own (same operator names, static device buffers, default stream).  Only
+    head size 128 with 16 query heads per kv head can run there (``kernel_v21.cuh:982-986``)."""
+    runner = os.path.join(ROOT, "oracle", "ref_cuda_runner.py")
+    if not os.path.exists(os.path.join(ROOT, "oracle", "_ref", "hogatt_ref.so")):
+        return {"unavailable": "the reference's CUDA extension was not built (no reference checkout at build time)"}
+    try:
+        res = subprocess.run([sys.executable, runner, "time", "--workload", workload, "--layers", str(layers), "--steps", "20",
+                              "--warmup", "5"], capture_output=True, text=True, timeout=300)
+        if res.returncode != 0:
+            return {"unavailable": (res.stderr.strip().splitlines() or ["failed"])[-1][:200]}
+        return json.loads(res.stdout.strip().splitlines()[-1])
+    except Exception as exc:                              # noqa: BLE001
+        return {"unavailable": str(exc)[:200]}
+
+
 def reference_runner(p: wl.Problem):
     """One call of the op on the host cores: the reference's own ``hogwild_sdpa_pt`` fed by its
     ``apply_rotary_pos_emb`` (python/hogwild/attention.py:38-67, :84-90, i.e. the eager branch :320-323) when the
@@ -583,7 +603,7 @@ def main():
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="target", choices=["target", "cfg2", "cfg3", "cfg4", "cfg5"])
+    ap.add_argument("--workload", default="target", choices=["target", "cfg2", "cfg3", "cfg4", "cfg5", "gqa16"])
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the additional long-context (cfg4) measurement")

@@ -188,6 +188,9 @@ BASELINE_CONFIGS: Dict[str, Dict] = {
     "cfg4": dict(W=2, Hq=32, Hkv=8, E=128, S=1, lengths=[131072, 4096, 4096], theta=5e5, dtype=torch.bfloat16),
     "cfg5": dict(W=8, Hq=64, Hkv=8, E=128, S=16, lengths=[16384] + [1024] * 8, theta=5e5, dtype=torch.bfloat16),
     "target": dict(W=4, Hq=32, Hkv=8, E=128, S=1, lengths=[8192] + [2048] * 4, theta=5e5, dtype=torch.bfloat16),
+    # the target's workers and lengths at the one head layout the reference's CUDA kernel accepts (16 query heads per
+    # kv head, src/kernels/kernel_v21.cuh:982): the shape both implementations can be timed on side by side
+    "gqa16": dict(W=4, Hq=32, Hkv=2, E=128, S=1, lengths=[8192] + [2048] * 4, theta=5e5, dtype=torch.bfloat16),
 }
 
 

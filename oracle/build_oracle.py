@@ -22,6 +22,7 @@ C_ORACLE = os.path.join(HERE, "libhogwild_oracle.so")
 REF_DIR = os.path.join(HERE, "_ref")
 REF_ROPE = os.path.join(REF_DIR, "librope_ref.so")
 REF_PY = os.path.join(REF_DIR, "hogwild", "attention.py")
+REF_CUDA = os.path.join(REF_DIR, "hogatt_ref.so")
 
 
 def _stale(out, srcs):
@@ -57,6 +58,42 @@ def build_ref(reference: str = None):
     return REF_ROPE
 
 
+def build_ref_cuda(reference: str = None, verbose: bool = False):
+    """The REFERENCE's own CUDA extension (``src/binding.cu`` + ``src/tpl/kernel_v21.cu``), compiled for sm_100a from
+    the checkout where it lies into ``oracle/_ref/hogatt_ref.so`` with one nvcc command (the reference's CMake build is
+    not run).  Its launcher only accepts head size 128 with 16 query heads per kv head (``kernel_v21.cuh:982-986``), so
+    it serves as a timed competitor and as the checker of the paged operators at such a shape, in a process of its
+    own (it registers the same ``libhogatt`` operator names as this package).  Returns the path, or ``None`` when
+    there is neither a checkout nor an earlier build."""
+    reference = reference or default_reference()
+    srcs = [os.path.join(reference, "src", "binding.cu"), os.path.join(reference, "src", "tpl", "kernel_v21.cu")]
+    if not all(os.path.exists(s) for s in srcs):
+        return REF_CUDA if os.path.exists(REF_CUDA) else None
+    deps = srcs + [os.path.join(reference, "src", "kernels", "kernel_v21.cuh")]
+    if not _stale(REF_CUDA, deps):
+        return REF_CUDA
+    import sysconfig
+    import torch
+    from torch.utils import cpp_extension as ce
+    os.makedirs(REF_DIR, exist_ok=True)
+    cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    inc = [os.path.join(reference, "src")] + ce.include_paths() + [sysconfig.get_paths()["include"]]
+    libs = ce.library_paths() + [os.path.join(cuda_home, "lib64")]
+    cmd = [os.path.join(cuda_home, "bin", "nvcc"), "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O3", "-lineinfo",
+           "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-shared", "-w",
+           "-DHOGDILD_ENABLE_FLOAT=1", "-DHOGDILD_ENABLE_HALF=1", "-DHOGDILD_ENABLE_BFLOAT=1",
+           f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}"]
+    cmd += [f"-I{i}" for i in inc] + srcs + ["-o", REF_CUDA] + [f"-L{d}" for d in libs]
+    cmd += ["-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-lcudart"]
+    cmd += [f"-Xlinker=-rpath,{d}" for d in libs]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        if verbose:
+            print(res.stdout[-3000:], res.stderr[-3000:])
+        return None
+    return REF_CUDA
+
+
 def load_reference_python():
     """The reference's ``hogwild.attention`` module from ``oracle/_ref`` (``None`` if it was never staged).
 
@@ -88,4 +125,4 @@ def load_reference_python():
 
 
 if __name__ == "__main__":
-    print(build_c_oracle(), build_ref())
+    print(build_c_oracle(), build_ref(), build_ref_cuda(verbose=True))

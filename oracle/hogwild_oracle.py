@@ -7,13 +7,15 @@ Only the test-suite, the smoke check and the CPU-baseline leg of the benchmark u
 
 Parity pin: the reference ships no golden vectors or tests for this path, so the oracle is
 pinned against outputs of the reference itself.  ``tests/golden/make_golden.py`` imports the
-reference's ``python/hogwild/attention.py`` in the build container, runs
+reference's ``python/hogwild/attention.py``, runs
 ``hogwild_sdpa_pt`` / ``apply_rotary_pos_emb`` on the seeded problems of
 ``inference_lib_b200.workloads`` and stores the results under ``tests/golden/``;
 ``tests/test_oracle.py`` checks every function below against those files.  The paged
 variants have no Python/CPU implementation in the reference at all: their oracle is by
-construction (gather the blocks into contiguous fragments, then the function below), and
-their parity is "unpinned".
+construction (gather the blocks into contiguous fragments, then the function below); it is
+pinned on the GPU instead, against the reference's own CUDA kernels recompiled for sm_100a
+at the one head layout they accept (``tests/test_gpu_reference_cuda.py``,
+``oracle/ref_cuda_runner.py``).
 
 Which reference lines each function follows:
 

@@ -78,7 +78,7 @@ def main():
     path = os.path.join(HERE, "reference_outputs.npz")
     store = dict(np.load(path)) if (only and os.path.exists(path)) else {}
 
-    jobs = [(n, lambda n=n: wl.baseline_problem(n)) for n in ("cfg1", "cfg2", "cfg3", "target", "cfg4")]
+    jobs = [(n, lambda n=n: wl.baseline_problem(n)) for n in ("cfg1", "cfg2", "cfg3", "target", "cfg4", "gqa16")]
     jobs += [(f"cfg5_g{g}", lambda g=g: wl.baseline_problem("cfg5", seed=g)) for g in range(4)]
     jobs += [(n, lambda n=n: wl.edge_problem(n)) for n in wl.EDGE_CASES]
     for name, build in jobs:
