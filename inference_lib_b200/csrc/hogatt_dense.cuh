@@ -14,14 +14,16 @@
 //   * K, V and Q tiles are fetched by TMA (cp.async.bulk.tensor, one tensor map per fragment, encoded on the
 //     host) into shared memory in the 128-byte-swizzled layout the tensor core reads directly.
 //   * S = Q K^T (128 x 128 x 128) and O += P V (128 x 128 x 128) are tcgen05.mma instructions issued by one
-//     thread; S (two buffers) and O live in tensor memory.  The softmax warps pull S out of tensor memory
-//     (tcgen05.ld), mask, exponentiate, write P as bf16/f16 into shared memory for the second MMA, and keep the
-//     running max and sum in registers.  O is rescaled in tensor memory only when a row's
+//     thread; S (two buffers), P and O live in tensor memory.  The softmax warps pull S out of tensor memory
+//     (tcgen05.ld), mask, exponentiate, write P as bf16/f16 back into tensor memory (tcgen05.st) -- the second MMA
+//     takes its A operand from there: no trip of P through shared memory, no proxy fence, and room for deeper K / V
+//     rings (measured 166 -> 157 us per 1,024-row group) -- and keep the running max and sum in registers.  (The query
+//     tile as a tensor-memory operand too was measured and is slower: 176 us.)  O is rescaled in tensor memory only when a row's
 //     max has grown by more than 2^8 since the scale it is stored at (then exp2 arguments stay below 8 and
 //     nothing overflows); the stored scale travels with the partial result, so the merge is exact.
 //
-// Warp roles (320 threads): warps 0-7 softmax, warp 8 issues the K/V copies, warp 9 allocates tensor memory, issues
-// the Q copies and every MMA.  Softmax warps w and w + 4 share the 32 query rows of tensor-memory lanes
+// Warp roles (352 threads): warps 0-7 softmax, warp 8 issues the K/V copies, warp 9 allocates tensor memory, issues
+// the Q copies and the S MMAs, warp 10 issues the PV MMAs.  Softmax warps w and w + 4 share the 32 query rows of tensor-memory lanes
 // 32 (w % 4) ... + 31 and split the 128 columns of S (keys) and of O between them: two warps per scheduler hide each
 // other's latencies, and a thread keeps 64 scores in registers.  Both derive the same row maximum -- each also
 // reads the other half's scores for that, which costs two more tensor-memory loads and no synchronisation -- so
@@ -43,7 +45,7 @@ constexpr int kDenseTile = 128;             // keys per tile (MMA N of S, K of P
 // beat four -- every warp re-reads the whole row for the maximum, so four warps issue 1.7 times the instructions.)
 constexpr int kDenseSplit = 2;
 constexpr int kDenseSoftmaxWarps = 4 * kDenseSplit;
-constexpr int kDenseThreads = (kDenseSoftmaxWarps + 2) * 32;
+constexpr int kDenseThreads = (kDenseSoftmaxWarps + 3) * 32;
 
 struct alignas(64) DenseMaps {
     CUtensorMap q;                          // [F, W, Hkv, G*S, E] view of the rotated queries
@@ -55,10 +57,9 @@ struct DenseCfg {
     static constexpr int HD = 128;
     static constexpr int ATOM_BYTES = 128 * 128;            // [128 rows][64 16-bit columns], rows of 128 bytes, swizzled
     static constexpr int TILE_BYTES = 2 * ATOM_BYTES;       // a 128 x 128 operand tile: two column halves
-    static constexpr int NK = 3, NV = 2;                    // K ring, V ring
+    static constexpr int NK = 3, NV = 3;                    // K ring, V ring
     static constexpr int OFF_Q = 0;
-    static constexpr int OFF_P = OFF_Q + TILE_BYTES;
-    static constexpr int OFF_K = OFF_P + TILE_BYTES;
+    static constexpr int OFF_K = OFF_Q + TILE_BYTES;
     static constexpr int OFF_V = OFF_K + NK * TILE_BYTES;
     static constexpr int OFF_BAR = OFF_V + NV * TILE_BYTES;                 // 224 KiB of tiles
     // barriers: q_full, k_full[NK], k_empty[NK], v_full[NV], v_empty[NV], s_full[2], s_free[2], p_full, o_done, l_ready[4]
@@ -67,7 +68,8 @@ struct DenseCfg {
     static constexpr int OFF_PLAN = OFF_MISC + 16;                          // vis[F], pre[F + 1]
     static constexpr int TMEM_COLS = 512;
     static constexpr int COL_O = 0, COL_S0 = 128, COL_S1 = 256;
-    static constexpr int COL_L = 384;           // 2 x 4 columns: the column groups' shares of the row sums, handed over at a flush
+    static constexpr int COL_P = 384;           // 64 columns: P, two 16-bit probabilities per 32-bit column
+    static constexpr int COL_L = 448;           // 2 x 4 columns: the column groups' shares of the row sums, handed over at a flush
 };
 
 __host__ __device__ inline size_t dense_smem_bytes(int F) {
@@ -94,6 +96,15 @@ __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// D[tmem] (+)= A[tmem] * B[smem]: A is 128 rows (lanes) x 16 k (8 columns, two 16-bit elements each, lower k in the low half)
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
 
@@ -309,91 +320,83 @@ dense_attention_kernel(const __grid_constant__ KernelArgs a, const __grid_consta
             }
         }
     } else if (warp == kDenseSoftmaxWarps + 1) {
-        // ============================== Q copies and every MMA ==============================
+        // ============================== Q copies and the S MMAs ==============================
+        // Issuing a tcgen05.mma costs the issuing thread some 60-70 cycles, sixteen of them per tile about as long as
+        // the tensor pipe needs to execute them -- so the two GEMMs of a tile are issued by two threads that only meet at
+        // barriers: this one runs ahead with S = Q K^T, the next warp follows the softmax warps with O += P V.
         if (lane == 0) {
             constexpr uint32_t IDESC_S = umma_idesc<T>(false, kDenseRows, kDenseTile);
-            constexpr uint32_t IDESC_O = umma_idesc<T>(true, kDenseRows, C::HD);
-            const uint32_t q_smem = sbase + C::OFF_Q, p_smem = sbase + C::OFF_P;
+            const uint32_t q_smem = sbase + C::OFF_Q;
             uint32_t q_phase = 0;
-            auto load_q = [&](const DenseTile& d) {
-                const int r0 = d.rb * kDenseRows;
-                mbar_arrive_expect_tx(q_full, C::TILE_BYTES);
-                tma_load_5d(q_smem, &maps.q, 0, r0 % GS, d.hkv, r0 / GS, d.f, q_full);
-                tma_load_5d(q_smem + C::ATOM_BYTES, &maps.q, 64, r0 % GS, d.hkv, r0 / GS, d.f, q_full);
-            };
-            // S_it = Q K^T into S buffer it & 1 (K ring stage it % NK); the stage is handed back when the MMAs are done
-            auto issue_s = [&](int it) -> bool {
+            // the matrix descriptors are built once (a k-step only moves the start-address field: +32 bytes inside a
+            // 64-column swizzle atom, +16 KiB to the second atom)
+            const uint64_t q_desc = umma_desc(q_smem, 16, 1024);
+            uint64_t k_desc[C::NK];
+#pragma unroll
+            for (int i = 0; i < C::NK; ++i) k_desc[i] = umma_desc(sbase + C::OFF_K + i * C::TILE_BYTES, 16, 1024);
+            DenseWalk walk(vis, pre, a.F, a.Hkv, t0, t1);
+            bool ok = true;
+            for (int it = 0; !walk.done() && ok; ++it) {
+                const DenseTile d = walk.next();
                 const int ks = it % C::NK, sb = it & 1;
-                if (!mbar_wait_bounded(k_full + 8 * ks, ((uint32_t)(it / C::NK)) & 1u, abort_flag, a.status, STATUS_WAIT_FULL_TIMEOUT))
-                    return false;
-                if (!mbar_wait_bounded(s_free + 8 * sb, (((uint32_t)(it >> 1)) & 1u) ^ 1u, abort_flag, a.status, STATUS_WAIT_SYNC_TIMEOUT))
-                    return false;
+                if (d.new_segment) {
+                    // the query tile changes: S_{it-1}, the last reader of the old one, must have finished
+                    if (it > 0)
+                        ok = mbar_wait_bounded(s_full + 8 * ((it - 1) & 1), ((uint32_t)((it - 1) >> 1)) & 1u, abort_flag, a.status,
+                                               STATUS_WAIT_SYNC_TIMEOUT);
+                    if (!ok) break;
+                    const int r0 = d.rb * kDenseRows;
+                    mbar_arrive_expect_tx(q_full, C::TILE_BYTES);
+                    tma_load_5d(q_smem, &maps.q, 0, r0 % GS, d.hkv, r0 / GS, d.f, q_full);
+                    tma_load_5d(q_smem + C::ATOM_BYTES, &maps.q, 64, r0 % GS, d.hkv, r0 / GS, d.f, q_full);
+                    ok = mbar_wait_bounded(q_full, q_phase, abort_flag, a.status, STATUS_WAIT_FULL_TIMEOUT);
+                    q_phase ^= 1u;
+                    if (!ok) break;
+                }
+                // S_it = Q K^T into S buffer it & 1 (K ring stage it % NK); the stage is handed back when the MMAs are done
+                ok = mbar_wait_bounded(k_full + 8 * ks, ((uint32_t)(it / C::NK)) & 1u, abort_flag, a.status, STATUS_WAIT_FULL_TIMEOUT) &&
+                     mbar_wait_bounded(s_free + 8 * sb, (((uint32_t)(it >> 1)) & 1u) ^ 1u, abort_flag, a.status, STATUS_WAIT_SYNC_TIMEOUT);
+                if (!ok) break;
                 tc_fence_after();
-                const uint32_t k_smem = sbase + C::OFF_K + ks * C::TILE_BYTES;
+                const uint64_t kd = ks == 0 ? k_desc[0] : (ks == 1 ? k_desc[1] : k_desc[2]);
                 const uint32_t d_tmem = tmem + (sb ? C::COL_S1 : C::COL_S0);
 #pragma unroll
                 for (int kk = 0; kk < C::HD / 16; ++kk) {
-                    const uint32_t off = (kk >> 2) * C::ATOM_BYTES + (kk & 3) * 32;
-                    tc_mma(d_tmem, umma_desc(q_smem + off, 16, 1024), umma_desc(k_smem + off, 16, 1024), IDESC_S, kk > 0);
+                    const uint64_t off = (uint64_t)(((kk >> 2) * C::ATOM_BYTES + (kk & 3) * 32) >> 4);
+                    tc_mma(d_tmem, q_desc + off, kd + off, IDESC_S, kk > 0);
                 }
                 tc_commit(s_full + 8 * sb);
                 tc_commit(k_empty + 8 * ks);
-                return true;
-            };
-
+                HOGATT_TL(0, 3000 + it);
+            }
+        }
+    } else if (warp == kDenseSoftmaxWarps + 2) {
+        // ============================== the O += P V MMAs ==============================
+        if (lane == 0) {
+            constexpr uint32_t IDESC_O = umma_idesc<T>(true, kDenseRows, C::HD);
+            uint64_t v_desc[C::NV];
+#pragma unroll
+            for (int i = 0; i < C::NV; ++i) v_desc[i] = umma_desc(sbase + C::OFF_V + i * C::TILE_BYTES, C::ATOM_BYTES, 1024);
             DenseWalk walk(vis, pre, a.F, a.Hkv, t0, t1);
             bool ok = true;
-            DenseTile cur, nxt;
-            bool have_next = !walk.done();
-            if (have_next) {
-                nxt = walk.next();
-                load_q(nxt);
-                ok = mbar_wait_bounded(q_full, q_phase, abort_flag, a.status, STATUS_WAIT_FULL_TIMEOUT);
-                q_phase ^= 1u;
-                ok = ok && issue_s(0);
-            }
-            for (int it = 0; have_next && ok; ++it) {
-                cur = nxt;
-                have_next = !walk.done();
-                bool reload = false;
-                if (have_next) {
-                    nxt = walk.next();
-                    reload = nxt.new_segment;
-                    if (!reload) {
-                        ok = issue_s(it + 1);
-                        HOGATT_TL(0, 3000 + it);
-                        if (!ok) break;
-                    } else {
-                        // the query tile changes: S_it must be finished with the old one before it is overwritten
-                        ok = mbar_wait_bounded(s_full + 8 * (it & 1), ((uint32_t)(it >> 1)) & 1u, abort_flag, a.status,
-                                               STATUS_WAIT_SYNC_TIMEOUT);
-                        if (!ok) break;
-                        load_q(nxt);
-                    }
-                }
-                HOGATT_TL(0, 1000 + it);
-                // O (+)= P_it V_it
+            for (int it = 0; !walk.done() && ok; ++it) {
+                const DenseTile cur = walk.next();
                 const int vs = it % C::NV;
                 ok = mbar_wait_bounded(p_full, ((uint32_t)it) & 1u, abort_flag, a.status, STATUS_WAIT_SYNC_TIMEOUT) &&
                      mbar_wait_bounded(v_full + 8 * vs, ((uint32_t)(it / C::NV)) & 1u, abort_flag, a.status, STATUS_WAIT_FULL_TIMEOUT);
                 if (!ok) break;
                 tc_fence_after();
-                const uint32_t v_smem = sbase + C::OFF_V + vs * C::TILE_BYTES;
+                const uint64_t vd = vs == 0 ? v_desc[0] : (vs == 1 ? v_desc[1] : v_desc[2]);
+                const uint32_t acc0 = cur.first_of_unit ? 0u : 1u;
 #pragma unroll
                 for (int kk = 0; kk < kDenseTile / 16; ++kk) {
-                    const uint32_t aoff = (kk >> 2) * C::ATOM_BYTES + (kk & 3) * 32;
-                    // V is [key][Ev]: Ev (the MMA's N) is contiguous -> MN-major; 16 keys per step = two 8-key swizzle atoms
-                    tc_mma(tmem + C::COL_O, umma_desc(p_smem + aoff, 16, 1024), umma_desc(v_smem + kk * 2048, C::ATOM_BYTES, 1024),
-                           IDESC_O, (kk > 0 || !cur.first_of_unit) ? 1u : 0u);
+                    // A = P from tensor memory: 16 keys are 8 columns.  V is [key][Ev]: Ev (the MMA's N) is contiguous ->
+                    // MN-major; 16 keys per step = two 8-key swizzle atoms (2 KiB)
+                    tc_mma_ts(tmem + C::COL_O, tmem + C::COL_P + kk * 8, vd + (uint64_t)(kk * 2048 >> 4), IDESC_O, kk > 0 ? 1u : acc0);
                 }
                 tc_commit(o_done);
                 tc_commit(v_empty + 8 * vs);
                 HOGATT_TL(0, 2000 + it);
-                if (reload) {
-                    ok = mbar_wait_bounded(q_full, q_phase, abort_flag, a.status, STATUS_WAIT_FULL_TIMEOUT);
-                    q_phase ^= 1u;
-                    ok = ok && issue_s(it + 1);
-                }
             }
         }
     } else {
@@ -404,9 +407,6 @@ dense_attention_kernel(const __grid_constant__ KernelArgs a, const __grid_consta
         const int part = warp >> 2;                            // which COLS columns of S, P and O this thread owns
         const int col0 = part * COLS;
         const uint32_t lane_base = ((uint32_t)((warp & 3) * 32)) << 16;
-        // this thread's 2 * COLS bytes of P inside the row's 128 bytes of a [128][64] swizzled atom
-        const uint32_t p_row = sbase + C::OFF_P + (col0 >> 6) * C::ATOM_BYTES + row * 128;
-        const int p_chunk0 = (col0 & 63) >> 3;                 // first 16-byte chunk (before the swizzle)
         const float scale2 = a.l2scale;                        // scores are raw dot products; exp2((s - m) * scale2)
         const float grow_by = 8.f / scale2;                    // raw-score distance that equals a factor 2^8
         float m_run = -INFINITY, l_run = 0.f;                  // running max (raw), this thread's share of the running sum
@@ -528,14 +528,10 @@ dense_attention_kernel(const __grid_constant__ KernelArgs a, const __grid_consta
                 tmem_wait_st();
             }
             if (warp == 0) HOGATT_TL(1, 5000 + it);
-            // ---- P (storage type) into shared memory, 128-byte swizzle: 16-byte chunk c of row r sits at c ^ (r & 7) ----
-#pragma unroll
-            for (int c = 0; c < COLS / 8; ++c) {
-                const uint32_t dst = p_row + (((p_chunk0 + c) ^ (row & 7)) << 4);
-                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(packed[4 * c]), "r"(packed[4 * c + 1]),
-                             "r"(packed[4 * c + 2]), "r"(packed[4 * c + 3])
-                             : "memory");
-            }
+            // ---- P (storage type, two per column) into tensor memory: this row's lane, this thread's columns ----
+            static_assert(COLS == 64, "one 32-column store of packed probabilities per thread");
+            tmem_st32(tmem + lane_base + C::COL_P + col0 / 2, *reinterpret_cast<const float(*)[32]>(&packed[0]));
+            tmem_wait_st();
             // V rows at or past the fragment's true length may hold anything (spare rows of a slab, fetched as they
             // are): their probabilities are exactly zero, but 0 * NaN would poison O.  Zero them in the staged tile
             // (each thread its share of the row's bytes).
@@ -549,8 +545,8 @@ dense_attention_kernel(const __grid_constant__ KernelArgs a, const __grid_consta
 #pragma unroll
                     for (int c = 0; c < COLS / 8; ++c) *reinterpret_cast<int4*>(vrow + c * 16) = make_int4(0, 0, 0, 0);
                 }
+                fence_proxy_async_smem();      // generic-proxy writes (V rows) before the MMA's async-proxy reads
             }
-            fence_proxy_async_smem();          // generic-proxy writes (P, V rows) before the MMA's async-proxy reads
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_full);
