@@ -17,8 +17,10 @@
 //     thread; S (two buffers), P and O live in tensor memory.  The softmax warps pull S out of tensor memory
 //     (tcgen05.ld), mask, exponentiate, write P as bf16/f16 back into tensor memory (tcgen05.st) -- the second MMA
 //     takes its A operand from there: no trip of P through shared memory, no proxy fence, and room for deeper K / V
-//     rings (measured 166 -> 157 us per 1,024-row group) -- and keep the running max and sum in registers.  (The query
-//     tile as a tensor-memory operand too was measured and is slower: 176 us.)  O is rescaled in tensor memory only when a row's
+//     rings (measured 166 -> 157 us per 1,024-row group) -- and keep the running max and sum in registers.  (Measured
+//     and not kept: the query tile as a tensor-memory operand too, 176 us; two query buffers with a segment-ahead fetch
+//     at the price of a two-stage K ring, +4 us; two softmax groups taking the tiles in turn, one thread per row,
+//     +20 us; programmatic dependent launch behind the rotation kernel, +3 us.)  O is rescaled in tensor memory only when a row's
 //     max has grown by more than 2^8 since the scale it is stored at (then exp2 arguments stay below 8 and
 //     nothing overflows); the stored scale travels with the partial result, so the merge is exact.
 //
