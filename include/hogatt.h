@@ -36,7 +36,9 @@ extern "C" {
 
 #define HOGATT_ABI_VERSION 2
 #ifndef HOGATT_MAX_FRAGMENTS
-#define HOGATT_MAX_FRAGMENTS 128   /* fragment table travels by value in the kernel arguments */
+#define HOGATT_MAX_FRAGMENTS 128   /* the fragment table travels by value in the kernel arguments (24 bytes per
+                                      fragment); the reference's device pointer table admits 512
+                                      (src/binding.cu:79-82).  More fragments: HOGATT_ERR_TOO_MANY_FRAGMENTS */
 #endif
 #define HOGATT_MAX_PEERS 8         /* GPUs of one node that can share a gathered output */
 
@@ -206,10 +208,14 @@ int hogatt_fused_launch(const hogatt_problem* p, hogatt_stream_t stream);
  *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
  *     that device current); make that first call outside any stream capture.  Later calls only
  *     enqueue kernels.  No call allocates or frees memory.
- *   - All calls on a device share the one array, which keeps whatever the last call left in it.  The
- *     kernels write every word of it before they read it, so nothing has to be cleared between
- *     calls, but two calls that overlap on the GPU (issued on different streams) race on it:
- *     serialise them, or give the overlapping ones their own workspace through hogatt_fused_launch.
+ *   - All calls on a device share the one array, which keeps whatever the last call left in it.
+ *     Nothing has to be cleared between calls: every partial slot that enters a result was written
+ *     by this call's attention kernel first.  The merge step does load slots this call did not
+ *     write (it reads a fixed number per row so that the loads are in flight together) and discards
+ *     them by the unit's slot count before any arithmetic, so stale bytes, NaN patterns included,
+ *     never reach an output.  Two calls that overlap on the GPU (issued on different streams) race
+ *     on the array: serialise them, or give the overlapping ones their own workspace through
+ *     hogatt_fused_launch.
  */
 #define HOGATT_STATIC_SCRATCH_BYTES (8u << 20)
 int hogatt_fused_launch_static(const hogatt_problem* p, hogatt_stream_t stream);

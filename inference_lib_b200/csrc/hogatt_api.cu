@@ -1,5 +1,6 @@
 // C ABI of libhogatt_b200.so (declared in include/hogatt.h): argument validation, kernel choice,
-// workspace carving and launches.  No allocation, no synchronisation, no hidden static buffers.
+// workspace carving and launches.  No allocation, no synchronisation, and no static device buffers, with one
+// declared exception: the fixed scratch array that hogatt_fused_launch_static uses in place of a workspace.
 #include <algorithm>
 #include <atomic>
 #include <cstdio>
@@ -82,14 +83,6 @@ bool pdl_enabled() {
         return !(v && v[0] == '0');
     }();
     return on;
-}
-
-int tune_flags() {
-    static const int v = [] {
-        const char* e = getenv("HOGATT_TUNE");
-        return e ? atoi(e) : 0;
-    }();
-    return v;
 }
 
 // HOGATT_DENSE=0 in the environment keeps AUTO away from the tcgen05 kernel (A/B measurements).
@@ -176,6 +169,8 @@ int resolve(const hogatt_problem* p, Resolved* r) {
     if (p->dtype != HOGATT_F32 && p->dtype != HOGATT_F16 && p->dtype != HOGATT_BF16) return HOGATT_ERR_UNSUPPORTED_DTYPE;
     const int64_t rows_total = (int64_t)p->W * (p->Hq / p->Hkv) * p->S;
     if (rows_total > (1 << 24) || (int64_t)p->F * p->W * p->S > (1 << 26)) return HOGATT_ERR_TOO_LARGE;
+    // the rotated-query side output [F,W,Hq,S,E] is indexed with 32-bit element counts in the kernels
+    if ((int64_t)p->F * p->W * p->Hq * p->S * std::max(p->E, 8) >= ((int64_t)1 << 31)) return HOGATT_ERR_TOO_LARGE;
     int kernel = p->kernel;
     r->cluster_mode = kernel == HOGATT_KERNEL_MMA ? -1 : (kernel == HOGATT_KERNEL_MMA_CLUSTER ? 1 : 0);
     r->cluster = 0;
@@ -428,13 +423,17 @@ int launch_fma_dims(const KernelArgs& args, int dev, int smem_optin, int grid, c
 // instead of one per 24 partials), as long as that grid stays small; otherwise the batched one-warp-per-row kernel.
 template <class T>
 int launch_merge(const KernelArgs& args, const Resolved& r, cudaStream_t stream) {
-    if (args.parts_per_unit > 32 && (int64_t)r.units * r.rows_per_block <= 4096 && !(tune_flags() & 2)) {
+    if (args.parts_per_unit > 32 && (int64_t)r.units * r.rows_per_block <= 4096) {
         dim3 wgrid((unsigned)r.units, (unsigned)r.rows_per_block);
         HOGATT_CUDA_OK(launch_kernel(merge_wide_kernel<T>, wgrid, dim3(kWideWarps * 32), 0, stream, args));
         return HOGATT_OK;
     }
     dim3 mgrid((unsigned)r.units, (unsigned)ceil_div(r.rows_per_block, kMergeWarps));
-    if (args.parts_per_unit <= 32)
+    if (args.parts_per_unit <= 4)           // units of many query rows, cut into few partials each: lean instantiations
+        HOGATT_CUDA_OK(launch_kernel(merge_kernel<T, 1, 4>, mgrid, dim3(kMergeWarps * 32), 0, stream, args));
+    else if (args.parts_per_unit <= 8)
+        HOGATT_CUDA_OK(launch_kernel(merge_kernel<T, 1, 8>, mgrid, dim3(kMergeWarps * 32), 0, stream, args));
+    else if (args.parts_per_unit <= 32)
         HOGATT_CUDA_OK(launch_kernel(merge_kernel<T, 1>, mgrid, dim3(kMergeWarps * 32), 0, stream, args));
     else
         HOGATT_CUDA_OK(launch_kernel(merge_kernel<T, 5>, mgrid, dim3(kMergeWarps * 32), 0, stream, args));
@@ -584,7 +583,9 @@ int rope_launch(void* rq, const void* queries, const float* cosines, const float
     const int64_t rows = (int64_t)F * W * Hq * S;
     if (rows > (1 << 30)) return HOGATT_ERR_TOO_LARGE;
     const int64_t work = rows * ((dtype != HOGATT_F32 && E % 8 == 0) ? E / 8 : E);      // chunks or channels
-    const unsigned blocks = (unsigned)std::min<int64_t>((work + 127) / 128, 1 << 16);
+    int64_t cap = 1 << 16;
+    if (const char* e = getenv("HOGATT_ROPE_CAP")) cap = atoi(e);
+    const unsigned blocks = (unsigned)std::min<int64_t>((work + 127) / 128, cap);
     switch (dtype) {
         case HOGATT_F32:
             rope_kernel<float><<<blocks, 128, 0, stream>>>((float*)rq, (const float*)queries, cosines, sines, F, W, Hq, S, E, rotary_dim);
@@ -658,7 +659,6 @@ int attention_launch(const hogatt_problem* p, bool fused, cudaStream_t stream, c
     args.ws_m = reinterpret_cast<float*>(ws + w.m);
     args.ws_l = reinterpret_cast<float*>(ws + w.l);
     args.status = p->device_status;
-    args.tune = tune_flags();
 #ifdef HOGATT_TIMELINE
     {
         static std::atomic<int> trace_counter{0};
@@ -932,7 +932,9 @@ int hogatt_copy_to_blocks_launch(const void* key_states, const void* value_state
     if (!aligned16(key_states) || !aligned16(value_states) || !aligned16(key_cache) || !aligned16(value_cache)) return HOGATT_ERR_MISALIGNED;
     if (S_new == 0) return HOGATT_OK;
     const int64_t total = (int64_t)B * Hkv * S_new * ((E + Ev) / vec);
-    const unsigned blocks = (unsigned)std::min<int64_t>((total + 255) / 256, 148 * 8);
+    int dev = 0, sms = 0, smem_optin = 0;
+    if (const int rc = current_device_info(&dev, &sms, &smem_optin)) return rc;
+    const unsigned blocks = (unsigned)std::min<int64_t>((total + 255) / 256, (int64_t)sms * 8);   // 8 CTAs of 256 threads per SM
     switch (dtype) {
         case HOGATT_F32:
             copy_to_blocks_kernel<float><<<blocks, 256, 0, stream>>>((const float*)key_states, (const float*)value_states, (float*)key_cache, (float*)value_cache, block_table, seq_lengths, B, Hkv, S_new, E, Ev, block_size, max_blocks);

@@ -37,7 +37,6 @@ struct KernelArgs {
     int host_plan, plan_tiles, plan_ctas;
     int stable_fragments;  // fragments [0, stable_fragments) may be fetched before griddepcontrol.wait
     int debug_id;          // tuning builds only: which slot of the event trace this call writes (0 otherwise)
-    int tune;              // HOGATT_TUNE from the environment (experiments; 0 in normal use)
     float l2scale;         // scale * log2(e): softmax runs in base 2
     void* out;
     void* rq;              // optional rotated-query output

@@ -20,12 +20,13 @@ constexpr int kMergeWarps = 4;
 // statistics and of the first batch have been issued for ALL slots, so that the count's own load shares
 // their round trip; what an unused slot returned is discarded (selected away, never multiplied).
 // One call handles 128 output columns (head sizes up to 128: the whole row); wider rows call it again.
-template <class T, int kMaxStat, class CountFn>
+template <class T, int kMaxStat, int kBatch, class CountFn>
 __device__ __forceinline__ void merge_partials_rows(const float* __restrict__ ws_o, const float* __restrict__ ws_m,
                                                    const float* __restrict__ ws_l, size_t slot0, int rpb, int Ev,
                                                    int row, int slots, CountFn count_of, T* const* bases, int nbases,
                                                    size_t offset, int lane, int e0) {
-    constexpr int kBatch = 24;
+    // kBatch: output partials fetched in the first round trip (24; 4 or 8 where a row never has more: a unit of
+    // many query rows is cut into few partials, and a lean kernel keeps 16 CTAs per SM resident instead of 3).
     // kMaxStat: statistics held per lane (32 * kMaxStat partials per row without extra loads)
     const int pstride = rpb * Ev;                    // floats between consecutive partials of a row (32-bit offsets: less code)
     float mp[kMaxStat], lp[kMaxStat];
@@ -91,7 +92,7 @@ __device__ __forceinline__ void merge_partials_rows(const float* __restrict__ ws
         }
         // more partials: one round trip per further batch.  The lean instantiation (at most 32 partials) only has
         // 8 left; it is kept small on purpose -- this kernel runs for 2.5 us and its instruction fetch shows.
-        constexpr int kNext = (kMaxStat == 1) ? 32 - kBatch : kBatch;
+        constexpr int kNext = (kMaxStat == 1 && kBatch > 16) ? 32 - kBatch : kBatch;
 #pragma unroll 1
         for (int p0 = kBatch; p0 < count; p0 += kNext) {
 #pragma unroll
@@ -132,7 +133,7 @@ __device__ __forceinline__ void merge_partials_rows(const float* __restrict__ ws
 // extra loads (kv heads sharded over GPUs: 37, 74, 148 partials per row); the host picks by the number of
 // partial slots per unit.  Two kernels rather than one with both paths: the bigger code cost the common
 // case +1 us per call (instruction fetch of a kernel that runs for 2.5 us).
-template <class T, int NSTAT>
+template <class T, int NSTAT, int KB = 24>
 __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const __grid_constant__ KernelArgs a) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int u = blockIdx.x;
@@ -141,9 +142,8 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const __grid_co
 #ifdef HOGATT_TIMELINE
     if (threadIdx.x == 0) atomicMin(&g_mtrace[a.debug_id % kTraceCalls][0], global_timer_ns_());
 #endif
-    if (!(a.tune & 1)) pdl_trigger();       // the next call's attention kernel may queue up behind this grid
+    pdl_trigger();       // the next call's attention kernel may queue up behind this grid
     pdl_wait();          // partials are complete and visible once the attention grid has finished
-    if (a.tune & 1) pdl_trigger();
     const int units = a.row_blocks * a.Hkv;
     const int RPB = a.rows_per_block, Ev = a.Ev;
     // how many CTAs left a partial for this unit: from the header the attention kernel wrote
@@ -169,7 +169,7 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const __grid_co
         const size_t offset = ((size_t)(id.w * hq_all + hq_off + hkv * a.G + id.g) * a.S + id.s) * Ev;
 #pragma unroll 1
         for (int e0 = 0; e0 < Ev; e0 += 128)
-            merge_partials_rows<T, NSTAT>(a.ws_o, a.ws_m, a.ws_l, (size_t)u * a.parts_per_unit, RPB, Ev, row, a.parts_per_unit,
+            merge_partials_rows<T, NSTAT, KB>(a.ws_o, a.ws_m, a.ws_l, (size_t)u * a.parts_per_unit, RPB, Ev, row, a.parts_per_unit,
                                           count_of, bases, nbases, offset, lane, e0);
     }
     HOGATT_SPAN_MAX(3);
@@ -190,9 +190,8 @@ __global__ void __launch_bounds__(kWideWarps * 32) merge_wide_kernel(const __gri
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int u = blockIdx.x, row = blockIdx.y;
     const int rb = u / a.Hkv, hkv = u % a.Hkv;
-    if (!(a.tune & 1)) pdl_trigger();
+    pdl_trigger();
     pdl_wait();
-    if (a.tune & 1) pdl_trigger();
     const int units = a.row_blocks * a.Hkv;
     const int RPB = a.rows_per_block, Ev = a.Ev;
     const int gr = rb * RPB + row;

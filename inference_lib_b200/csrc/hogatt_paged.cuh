@@ -202,7 +202,7 @@ __global__ void __launch_bounds__(kMergeWarps * 32) paged_merge_kernel(const __g
         const int splits = a.splits;
 #pragma unroll 1
         for (int e0 = 0; e0 < a.Ev; e0 += 128)
-            merge_partials_rows<T, 1>(a.ws_o, a.ws_m, a.ws_l, (size_t)blockIdx.x * a.splits, kFmaRows, a.Ev, row, splits,
+            merge_partials_rows<T, 1, 24>(a.ws_o, a.ws_m, a.ws_l, (size_t)blockIdx.x * a.splits, kFmaRows, a.Ev, row, splits,
                                       [splits]() { return splits; }, &out, 1,
                                       (size_t)(u.w * a.o_w + s_abs * a.o_s + hq * a.o_h), lane, e0);
     }

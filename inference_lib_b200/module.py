@@ -9,7 +9,7 @@ stay ``torch.nn.Linear`` (cuBLAS): they are plain GEMMs and not part of the path
 """
 from __future__ import annotations
 
-from typing import Optional, Tuple
+from typing import Optional, Sequence, Tuple
 
 import torch
 from torch import nn
@@ -52,10 +52,29 @@ class HogwildAttention(nn.Module):
         return m
 
     def forward(self, hidden_states: torch.Tensor, position_embeddings: Tuple[torch.Tensor, torch.Tensor],
-                cache: FragmentCache, new_rows: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """``hidden_states [W,S,hidden]``; ``position_embeddings`` = (cos, sin) ``[W,S,R]`` at the tokens' own
-        positions, as the model computes them; ``new_rows [W]`` int32 device for left-masked inputs."""
+                attention_mask: Optional[torch.Tensor] = None, past_key_values: Optional[FragmentCache] = None,
+                position_ids: Optional[torch.Tensor] = None, **kwargs) -> Tuple[torch.Tensor, None]:
+        """The call a decoder layer makes (``attention.py:291-336``; the keyword names are those of the
+        transformers release installed here, where the reference's ``past_key_value`` is ``past_key_values``).
+
+        ``hidden_states [W,S,hidden]``; ``position_embeddings`` = (cos, sin) ``[W,S,R]`` at the tokens' own
+        positions, as the model's ``rotary_emb`` computes them; ``attention_mask`` ``None`` or the ``[W,S]`` 0/1
+        left-padding mask, passed through by the model untouched: only the last ``sum(mask[w])`` tokens of worker
+        ``w`` enter the cache (``attention.py:148-154``).  Returns ``(attn_output, None)`` like the reference."""
+        cache = past_key_values if past_key_values is not None else kwargs.get("past_key_value")
+        if not isinstance(cache, FragmentCache):
+            raise TypeError("HogwildAttention needs a FragmentCache as past_key_values")
         W, S, _ = hidden_states.shape
+        if W != 1 and position_ids is None and "new_rows" not in kwargs:
+            # the reference's assertion (attention.py:304-305): several workers never share default positions
+            raise ValueError("when processing multiple workers, position_ids are mandatory")
+        if position_ids is not None and tuple(position_ids.shape) != (W, S):
+            raise ValueError(f"position_ids {tuple(position_ids.shape)} must match hidden_states {(W, S)}")
+        new_rows = kwargs.get("new_rows")
+        if attention_mask is not None:
+            if attention_mask.dim() != 2 or tuple(attention_mask.shape) != (W, S):
+                raise ValueError("attention_mask must be the [W,S] padding mask (left-padded), not an expanded one")
+            new_rows = attention_mask.sum(dim=1).to(torch.int32)
         shape = (W, S, -1, self.head_dim)
         q = self.q_proj(hidden_states).view(shape).transpose(1, 2)          # [W,Hq,S,D] views, no copies
         k = self.k_proj(hidden_states).view(shape).transpose(1, 2)
@@ -63,10 +82,53 @@ class HogwildAttention(nn.Module):
         cos, sin = position_embeddings
         cs = cache.update(k, v, self.layer_idx, cos, sin, new_rows)         # rotates the keys itself
         F = len(cs.keys)
-        if self._rq is None or self._rq.shape != (F, W, self.num_heads, S, self.head_dim):
+        if self._rq is None or self._rq.shape != (F, W, self.num_heads, S, self.head_dim) or self._rq.dtype != q.dtype:
             self._rq = torch.empty((F, W, self.num_heads, S, self.head_dim), dtype=q.dtype, device=q.device)
             self._att = torch.empty((W, self.num_heads, S, cs.values[0].shape[-1]), dtype=q.dtype, device=q.device)
         att = ops.hogwild_fused_planned(q, cs.loc, cs.keys, cs.values, self.scaling, cs.frags, cs.cos, cs.sin,
                                         rotated_queries=self._rq, out=self._att, host_lengths=cs.host_lengths,
                                         stable_fragments=cs.stable)
-        return self.o_proj(att.transpose(1, 2).reshape(W, S, -1))
+        return self.o_proj(att.transpose(1, 2).reshape(W, S, -1)), None
+
+
+def model_surgery(model) -> None:
+    """Swap every decoder layer's attention for :class:`HogwildAttention`, adopting its projections: the
+    reference's ``model_surgery`` (``attention.py:339-354``).
+
+    The reference also replaces the model's ``_update_causal_mask`` so that the 2-D padding mask reaches the
+    layers as it is.  The transformers release installed here has no such hook: its decoder skips mask
+    construction when ``attention_mask`` already is a dict of per-layer-type masks, which is what
+    :func:`decode_step` passes."""
+    cfg = model.model.config
+    for layer in model.model.layers:
+        old = layer.self_attn
+        layer.self_attn = HogwildAttention.from_projections(
+            old.q_proj, old.k_proj, old.v_proj, old.o_proj, num_heads=cfg.num_attention_heads,
+            num_kv_heads=cfg.num_key_value_heads, layer_idx=old.layer_idx)
+
+
+def decode_step(model, input_ids: torch.Tensor, position_ids: torch.Tensor, cache: FragmentCache,
+                attention_mask: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One forward of a model after :func:`model_surgery`: ``input_ids`` / ``position_ids`` ``[W,S]`` (one row per
+    worker, positions = the row indices the tokens get in the worker's own fragment), ``attention_mask`` ``None``
+    or the ``[W,S]`` left-padding mask.  Returns the logits ``[W,S,vocab]``.  Nothing is read back from the
+    device: a step can be captured into a CUDA graph."""
+    layer_types = set(getattr(model.model.config, "layer_types", None) or ["full_attention"])
+    masks = {t: attention_mask for t in layer_types}
+    hidden = model.model(input_ids=input_ids, position_ids=position_ids, attention_mask=masks, past_key_values=cache,
+                         use_cache=True).last_hidden_state
+    return model.lm_head(hidden)
+
+
+def cache_for_model(model, capacities: Sequence[int], order: Sequence[Sequence[int]],
+                    write_to: Optional[Sequence[int]] = None) -> FragmentCache:
+    """A :class:`FragmentCache` shaped for ``model``: layer count, kv heads, head size, the rotary frequencies and
+    attention scaling of its ``rotary_emb`` (what the reference reads through ``HogwildCache(model=...)``,
+    ``attention.py:113-121,199``)."""
+    cfg = model.model.config
+    head_dim = getattr(cfg, "head_dim", None) or cfg.hidden_size // cfg.num_attention_heads
+    rope = model.model.rotary_emb
+    p = next(model.parameters())
+    return FragmentCache(layers=cfg.num_hidden_layers, capacities=capacities, Hkv=cfg.num_key_value_heads, E=head_dim,
+                         dtype=p.dtype, device=p.device, order=order, write_to=write_to, inv_freq=rope.inv_freq,
+                         attention_scaling=float(getattr(rope, "attention_scaling", 1.0)))

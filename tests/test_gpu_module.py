@@ -1,5 +1,9 @@
 """The attention layer (projections + cache update + fused attention + output projection) over a few decode
-steps, against the same computation restated on the CPU with the oracles."""
+steps, against the same computation restated on the CPU with the oracles.
+
+The attention result is compared BEFORE the output projection, at the op's own tolerance (16-bit output against
+the fp32 oracle: max-abs <= 2e-2, mean-abs <= 2e-3; fp32: 1e-4), on the q/k/v the layer's own projections gave;
+the projected output is compared as well, against the oracle's result sent through the same projection."""
 import numpy as np
 import pytest
 import torch
@@ -11,8 +15,9 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-@pytest.mark.parametrize("dtype,head_dim,tol", [(torch.bfloat16, 128, 6e-2), (torch.float32, 64, 5e-4)])
-def test_attention_layer_matches_the_cpu_restatement(dtype, head_dim, tol):
+@pytest.mark.parametrize("dtype,head_dim,tol,tol_mean", [(torch.bfloat16, 128, 2e-2, 2e-3), (torch.float16, 64, 2e-2, 2e-3),
+                                                         (torch.float32, 64, 1e-4, 1e-5)])
+def test_attention_layer_matches_the_cpu_restatement(dtype, head_dim, tol, tol_mean):
     from inference_lib_b200.cache import FragmentCache
     from inference_lib_b200.module import HogwildAttention
     torch.manual_seed(3)
@@ -37,13 +42,13 @@ def test_attention_layer_matches_the_cpu_restatement(dtype, head_dim, tol):
         h = torch.randn(W, S, hidden, generator=g).to(dtype)
         x_gpu, x_cpu = h.to(DEV), h
         for l in range(layers):
-            y = mods[l](x_gpu, (kcos.to(DEV), ksin.to(DEV)), cache)
-            # ---- the same layer on the CPU ----
+            y, weights = mods[l](x_gpu, (kcos.to(DEV), ksin.to(DEV)), None, cache, position_ids=torch.from_numpy(pos).to(DEV))
+            assert weights is None
+            # ---- the same layer on the CPU, from the q/k/v its projections gave ----
             p = cpu[l]
             lin = lambda x, w, b=None: torch.nn.functional.linear(x, w, b)
-            q = lin(x_cpu, p["q_proj.weight"], p["q_proj.bias"]).view(W, S, Hq, head_dim).transpose(1, 2)
-            k = lin(x_cpu, p["k_proj.weight"], p["k_proj.bias"]).view(W, S, Hkv, head_dim).transpose(1, 2)
-            v = lin(x_cpu, p["v_proj.weight"], p["v_proj.bias"]).view(W, S, Hkv, head_dim).transpose(1, 2)
+            q, k, v = (proj(x_gpu).view(W, S, -1, head_dim).transpose(1, 2).cpu()
+                       for proj in (mods[l].q_proj, mods[l].k_proj, mods[l].v_proj))
             k_rot = oc.rotate_keys(k, kcos, ksin)
             for w in range(W):
                 f = 1 + w
@@ -53,11 +58,12 @@ def test_attention_layer_matches_the_cpu_restatement(dtype, head_dim, tol):
             cos, sin = oc.rotary_tables(loc, inv_freq.numpy(), 1.0, dtype)
             att, _ = oracle.fused(q.contiguous(), cos, sin, torch.from_numpy(loc), [t[None] for t in frag_k[l]],
                                   [t[None] for t in frag_v[l]], head_dim ** -0.5)
-            y_ref = lin(att.to(dtype).transpose(1, 2).reshape(W, S, -1), p["o_proj.weight"])
             torch.cuda.synchronize()
             assert int(cache.status.item()) == 0
             assert cache.frags(l).tolist() == now
-            diff = (y.float().cpu() - y_ref.float()).abs().max().item()
-            assert diff <= tol, (step, l, diff)
+            diff = (mods[l]._att.float().cpu() - att).abs()
+            assert diff.max().item() <= tol and diff.mean().item() <= tol_mean, (step, l, diff.max().item(), diff.mean().item())
+            y_ref = lin(att.to(dtype).transpose(1, 2).reshape(W, S, -1), p["o_proj.weight"])
+            assert (y.float().cpu() - y_ref.float()).abs().max().item() <= 3 * tol
             x_gpu, x_cpu = y, y.cpu()                     # next layer continues from the GPU's output on both sides
         own_len = [n + S for n in own_len]
