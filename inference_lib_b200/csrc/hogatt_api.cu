@@ -581,11 +581,24 @@ bool aligned16(const void* p) { return ((uintptr_t)p & 15u) == 0; }
 int rope_launch(void* rq, const void* queries, const float* cosines, const float* sines, int F, int W, int Hq, int S, int E,
                 int rotary_dim, int dtype, cudaStream_t stream) {
     const int64_t rows = (int64_t)F * W * Hq * S;
-    if (rows > (1 << 30)) return HOGATT_ERR_TOO_LARGE;
+    if (rows > (1 << 30) || rows * std::max(E, 8) >= ((int64_t)1 << 31)) return HOGATT_ERR_TOO_LARGE;   // 32-bit element counts
     const int64_t work = rows * ((dtype != HOGATT_F32 && E % 8 == 0) ? E / 8 : E);      // chunks or channels
-    int64_t cap = 1 << 16;
-    if (const char* e = getenv("HOGATT_ROPE_CAP")) cap = atoi(e);
-    const unsigned blocks = (unsigned)std::min<int64_t>((work + 127) / 128, cap);
+    if (dtype != HOGATT_F32 && rotary_dim == E && E % 16 == 0 && aligned16(cosines) && aligned16(sines) && aligned16(queries) &&
+        aligned16(rq)) {
+        // whole head rotated: a thread per pair of partner chunks, tables kept in registers over kRopeHeads heads
+        const int64_t items = (int64_t)F * W * S * (E / 16);
+        const dim3 grid((unsigned)((items + 127) / 128), (unsigned)ceil_div(Hq, kRopeHeads));
+        if (dtype == HOGATT_F16)
+            rope_pairs_kernel<__half><<<grid, 128, 0, stream>>>((__half*)rq, (const __half*)queries, cosines, sines, F, W, Hq, S, E);
+        else
+            rope_pairs_kernel<__nv_bfloat16><<<grid, 128, 0, stream>>>((__nv_bfloat16*)rq, (const __nv_bfloat16*)queries, cosines, sines, F, W, Hq, S, E);
+        HOGATT_CUDA_OK(cudaGetLastError());
+        return HOGATT_OK;
+    }
+    // one pass of four chunks per thread where there is enough work: 16 CTAs of 128 threads per SM
+    int dev = 0, sms = 0, smem_optin = 0;
+    if (const int rc = current_device_info(&dev, &sms, &smem_optin)) return rc;
+    const unsigned blocks = (unsigned)std::min<int64_t>((work + 127) / 128, (int64_t)sms * 16);
     switch (dtype) {
         case HOGATT_F32:
             rope_kernel<float><<<blocks, 128, 0, stream>>>((float*)rq, (const float*)queries, cosines, sines, F, W, Hq, S, E, rotary_dim);

@@ -360,4 +360,67 @@ __global__ void __launch_bounds__(128) rope_kernel(T* __restrict__ rq, const T* 
                              gridDim.x * blockDim.x);
 }
 
+// The same for 16-bit types with the whole head rotated (R == E, E a multiple of 16): a thread owns one pair of
+// 16-byte chunks (channels 8j.. and E/2 + 8j.., each the other's rotation partner) of one (f, w, s), keeps their four
+// table chunks in registers and walks kRopeHeads query heads with them: per 32 output bytes two 16-byte loads
+// instead of twelve.  Arithmetic and rounding are rotate_chunk's, so the bits are the same.
+constexpr int kRopeHeads = 4;
+template <class T>
+__global__ void __launch_bounds__(128) rope_pairs_kernel(T* __restrict__ rq, const T* __restrict__ q,
+                                                         const float* __restrict__ cosines, const float* __restrict__ sines,
+                                                         int F, int W, int Hq, int S, int E) {
+    const int pairs = E >> 4, half = E >> 1;
+    const int item = blockIdx.x * blockDim.x + threadIdx.x;
+    if (item >= F * W * S * pairs) return;
+    const int j = item % pairs;
+    int t = item / pairs;
+    const int s = t % S;
+    t /= S;
+    const int w = t % W, f = t / W;
+    const size_t tab = ((size_t)(f * W + w) * S + s) * E + 8 * j;
+    float cl[8], sl[8], chh[8], shh[8];
+    *reinterpret_cast<float4*>(cl) = *reinterpret_cast<const float4*>(cosines + tab);
+    *reinterpret_cast<float4*>(cl + 4) = *reinterpret_cast<const float4*>(cosines + tab + 4);
+    *reinterpret_cast<float4*>(sl) = *reinterpret_cast<const float4*>(sines + tab);
+    *reinterpret_cast<float4*>(sl + 4) = *reinterpret_cast<const float4*>(sines + tab + 4);
+    *reinterpret_cast<float4*>(chh) = *reinterpret_cast<const float4*>(cosines + tab + half);
+    *reinterpret_cast<float4*>(chh + 4) = *reinterpret_cast<const float4*>(cosines + tab + half + 4);
+    *reinterpret_cast<float4*>(shh) = *reinterpret_cast<const float4*>(sines + tab + half);
+    *reinterpret_cast<float4*>(shh + 4) = *reinterpret_cast<const float4*>(sines + tab + half + 4);
+    const int h0 = blockIdx.y * kRopeHeads;
+    uint4 xl[kRopeHeads], xh[kRopeHeads];
+#pragma unroll
+    for (int k = 0; k < kRopeHeads; ++k) {
+        const int h = min(h0 + k, Hq - 1);
+        const T* row = q + ((size_t)(w * Hq + h) * S + s) * E + 8 * j;
+        xl[k] = *reinterpret_cast<const uint4*>(row);
+        xh[k] = *reinterpret_cast<const uint4*>(row + half);
+    }
+#pragma unroll
+    for (int k = 0; k < kRopeHeads; ++k) {
+        if (h0 + k >= Hq) break;
+        const T* a = reinterpret_cast<const T*>(&xl[k]);
+        const T* b = reinterpret_cast<const T*>(&xh[k]);
+        uint4 lo, hi;
+        uint32_t* ol = reinterpret_cast<uint32_t*>(&lo);
+        uint32_t* oh = reinterpret_cast<uint32_t*>(&hi);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            float rl[2], rh[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int c = 2 * i + e;
+                const float av = Scalar<T>::to_float(a[c]), bv = Scalar<T>::to_float(b[c]);
+                rl[e] = __fsub_rn(__fmul_rn(av, cl[c]), __fmul_rn(bv, sl[c]));
+                rh[e] = __fadd_rn(__fmul_rn(bv, chh[c]), __fmul_rn(av, shh[c]));
+            }
+            ol[i] = pack2<T>(rl[0], rl[1]);
+            oh[i] = pack2<T>(rh[0], rh[1]);
+        }
+        T* dst = rq + ((size_t)((f * W + w) * Hq + h0 + k) * S + s) * E + 8 * j;
+        *reinterpret_cast<uint4*>(dst) = lo;
+        *reinterpret_cast<uint4*>(dst + half) = hi;
+    }
+}
+
 }  // namespace hogatt
