@@ -37,10 +37,10 @@ from inference_lib_b200 import workloads as wl  # noqa: E402
 METRIC = "hogwild attn achieved HBM TB/s (us/call in us_per_call)"
 UNIT = "TB/s"
 NOMINAL_HBM_GBS = 8000.0
-# dram__bytes_read.sum + dram__bytes_write.sum of the attention kernel divided by its algorithmic bytes, from the
-# ncu capture summarised in profiles/mma_attention_kernel_target.md (67.248 MB + 0.62 MB against 67.174 MB).
-# DRAM traffic of this kernel grows in proportion to the keys read, so other shapes are scaled by it.
-NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1.0103
+# dram__bytes_read.sum + dram__bytes_write.sum of the attention kernel divided by its algorithmic bytes, per workload,
+# from the ncu captures summarised under profiles/ (mma_attention_kernel_target.md, ..._cfg2_cfg3_cfg4.md).  Only a
+# single-GPU run of a captured shape at its full length reports `traffic`; everything else reports null.
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = {"target": 1.0146, "cfg2": 1.0017, "cfg3": 1.0191, "cfg4": 1.0082}
 FALLBACK_HBM_GBS = 6650.0
 
 
@@ -389,7 +389,9 @@ def run_ours(args):
                           "achieved_TFLOPs_per_gpu": round(flops / world / t_kernel / 1e12, 1),
                           "frac": round(flops / world / t_kernel / 1e12 / tf_peak, 4), "peak_TFLOPs": tf_peak})
             else:
-                e.update({"bound": "hbm", "frac": round(x["bytes_per_call"] / world / t_kernel / 1e9 / hbm_peak, 4)})
+                r = NCU_TRAFFIC_PER_ALGORITHMIC_BYTE.get(name) if world == 1 else None
+                e.update({"bound": "hbm", "frac": round(x["bytes_per_call"] / world / t_kernel / 1e9 / hbm_peak, 4),
+                          "traffic": int(x["bytes_per_call"] * r) if r else None})
             if name == "gqa16" and world == 1:
                 # the one head layout the reference's own CUDA kernel accepts: race it on the same GPU, same inputs
                 e["reference_cuda_kernel"] = race_reference_kernel(name, layers)
@@ -410,6 +412,10 @@ def run_ours(args):
     if tensor_bound:
         tf_peak, tf_src = measured_peak("bf16_tflops_sustained", FALLBACK_BF16_TFLOPS_SUSTAINED)
         tf = wl.baseline_problem(args.workload).flops() / world / ((secs_attn or secs) / n_calls) / 1e12
+    ratio = NCU_TRAFFIC_PER_ALGORITHMIC_BYTE.get(args.workload) if world == 1 and LENGTH_SCALE == 1.0 else None
+    traffic = int(per_gpu_bytes * ratio) if ratio else None
+    traffic_src = (f"ncu capture of this shape (profiles/): {ratio} x algorithmic bytes" if ratio
+                   else "no ncu capture of this shape / shard")
     line = {
         "metric": METRIC, "value": round(value, 4), "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(secs / args.steps * 1e3, 5), "higher_is_better": True,
@@ -425,8 +431,8 @@ def run_ours(args):
         "clocks": clocks,
         "e2e": e2e,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
-                     "frac": round(achieved / peak, 4), "traffic": int(per_gpu_bytes * NCU_TRAFFIC_PER_ALGORITHMIC_BYTE),
-                     "traffic_source": "ncu capture at the target shape, scaled by algorithmic bytes", "peak_source": peak_src,
+                     "frac": round(achieved / peak, 4), "traffic": traffic,
+                     "traffic_source": traffic_src, "peak_source": peak_src,
                      "kernel": "mma_attention_kernel (+ merge_kernel in the same interval)",
                      "bytes_per_launch": int(per_gpu_bytes)},
     }
