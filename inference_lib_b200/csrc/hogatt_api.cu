@@ -425,7 +425,14 @@ template <class T>
 int launch_merge(const KernelArgs& args, const Resolved& r, cudaStream_t stream) {
     if (args.parts_per_unit > 32 && (int64_t)r.units * r.rows_per_block <= 4096) {
         dim3 wgrid((unsigned)r.units, (unsigned)r.rows_per_block);
-        HOGATT_CUDA_OK(launch_kernel(merge_wide_kernel<T>, wgrid, dim3(kWideWarps * 32), 0, stream, args));
+        // Four warps (128 threads x 128 registers) fit on an SM beside a resident attention CTA, eight do not: with
+        // up to 24 partials per warp in one round trip, four serve up to 96 partials per row (kv heads over 2 or 4
+        // GPUs: 39, 76; measured 15.6 -> 14.4 us per call for one of two ranks' share at 16 K keys); a unit cut into
+        // 148 partials needs the eight (four take two round trips: 8.7 -> 9.3 us).
+        if (args.parts_per_unit <= 4 * 24)
+            HOGATT_CUDA_OK(launch_kernel(merge_wide_kernel<T, 4>, wgrid, dim3(4 * 32), 0, stream, args));
+        else
+            HOGATT_CUDA_OK(launch_kernel(merge_wide_kernel<T>, wgrid, dim3(kWideWarps * 32), 0, stream, args));
         return HOGATT_OK;
     }
     dim3 mgrid((unsigned)r.units, (unsigned)ceil_div(r.rows_per_block, kMergeWarps));
@@ -433,8 +440,14 @@ int launch_merge(const KernelArgs& args, const Resolved& r, cudaStream_t stream)
         HOGATT_CUDA_OK(launch_kernel(merge_kernel<T, 1, 4>, mgrid, dim3(kMergeWarps * 32), 0, stream, args));
     else if (args.parts_per_unit <= 8)
         HOGATT_CUDA_OK(launch_kernel(merge_kernel<T, 1, 8>, mgrid, dim3(kMergeWarps * 32), 0, stream, args));
-    else if (args.parts_per_unit <= 32)
-        HOGATT_CUDA_OK(launch_kernel(merge_kernel<T, 1>, mgrid, dim3(kMergeWarps * 32), 0, stream, args));
+    else if (args.parts_per_unit <= 32) {
+        // Two warps per CTA: 64 threads x 156 registers fit on an SM BESIDE a resident attention CTA (192 threads x 255
+        // registers leave 16 K registers), four warps do not.  With programmatic dependent launch that decides whether
+        // this grid is already resident when the attention grid drains, and whether the next call's attention CTAs can
+        // start on the SMs this grid occupies (measured: 18.8 -> 17.2 us per call at 16 K keys, 24.2 -> 22.2 at GQA 5).
+        dim3 g2((unsigned)r.units, (unsigned)ceil_div(r.rows_per_block, 2));
+        HOGATT_CUDA_OK(launch_kernel(merge_kernel<T, 1, 24, 2>, g2, dim3(64), 0, stream, args));
+    }
     else
         HOGATT_CUDA_OK(launch_kernel(merge_kernel<T, 5>, mgrid, dim3(kMergeWarps * 32), 0, stream, args));
     return HOGATT_OK;
@@ -675,7 +688,7 @@ int attention_launch(const hogatt_problem* p, bool fused, cudaStream_t stream, c
 #ifdef HOGATT_TIMELINE
     {
         static std::atomic<int> trace_counter{0};
-        args.debug_id = trace_counter.fetch_add(1) % kTraceCalls;
+    args.debug_id = trace_counter.fetch_add(1) % kTraceCalls;
     }
 #endif
     if (peers) {

@@ -280,10 +280,6 @@ __device__ __forceinline__ void bulk_load_hint(uint32_t dst_smem, const void* sr
         "l"(src), "r"(bytes), "r"(bar), "l"(policy)
         : "memory");
 }
-// Ask for `bytes` (a multiple of 16) at `src` to be brought into L2; nothing is waited for.
-__device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes) {
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
-}
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {
     uint64_t pol;
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));

@@ -133,8 +133,8 @@ __device__ __forceinline__ void merge_partials_rows(const float* __restrict__ ws
 // extra loads (kv heads sharded over GPUs: 37, 74, 148 partials per row); the host picks by the number of
 // partial slots per unit.  Two kernels rather than one with both paths: the bigger code cost the common
 // case +1 us per call (instruction fetch of a kernel that runs for 2.5 us).
-template <class T, int NSTAT, int KB = 24>
-__global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const __grid_constant__ KernelArgs a) {
+template <class T, int NSTAT, int KB = 24, int MW = kMergeWarps>
+__global__ void __launch_bounds__(MW * 32) merge_kernel(const __grid_constant__ KernelArgs a) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int u = blockIdx.x;
     const int rb = u / a.Hkv, hkv = u % a.Hkv;
@@ -162,7 +162,7 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const __grid_co
     const int hq_all = a.world > 0 ? a.world * a.Hq : a.Hq;       // heads of the destination tensor
     const int hq_off = a.world > 0 ? a.rank * a.Hq : 0;           // where this rank's heads start in it
 #pragma unroll 1
-    for (int row = blockIdx.y * kMergeWarps + warp; row < RPB; row += gridDim.y * kMergeWarps) {
+    for (int row = blockIdx.y * MW + warp; row < RPB; row += gridDim.y * MW) {
         const int gr = rb * RPB + row;
         if (gr >= a.rows_total) continue;
         const RowId id = decode_row(gr, a.G, a.S);
@@ -183,10 +183,10 @@ __global__ void __launch_bounds__(kMergeWarps * 32) merge_kernel(const __grid_co
 // maximum, denominator and weighted sum: one memory round trip for up to 192 partials per row), the eight results are
 // combined through shared memory.  The one-warp-per-row kernel above needs a round trip per 24 partials.
 constexpr int kWideWarps = 8;
-template <class T>
-__global__ void __launch_bounds__(kWideWarps * 32) merge_wide_kernel(const __grid_constant__ KernelArgs a) {
-    __shared__ float sm_m[kWideWarps], sm_l[kWideWarps];
-    __shared__ float4 sm_o[kWideWarps][64];               // up to 256 output columns
+template <class T, int WW = kWideWarps>
+__global__ void __launch_bounds__(WW * 32) merge_wide_kernel(const __grid_constant__ KernelArgs a) {
+    __shared__ float sm_m[WW], sm_l[WW];
+    __shared__ float4 sm_o[WW][64];               // up to 256 output columns
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int u = blockIdx.x, row = blockIdx.y;
     const int rb = u / a.Hkv, hkv = u % a.Hkv;
@@ -207,9 +207,9 @@ __global__ void __launch_bounds__(kWideWarps * 32) merge_wide_kernel(const __gri
     float M = -INFINITY, L = 0.f;
     float4 acc[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};     // columns lane*4 (+128)
 #pragma unroll 1
-    for (int p0 = warp; p0 < count; p0 += kWideWarps * kPer) {
+    for (int p0 = warp; p0 < count; p0 += WW * kPer) {
         // this pass: partials p0, p0 + 8, ...; lane k holds the statistics of the k-th of them
-        const int mine = p0 + lane * kWideWarps;
+        const int mine = p0 + lane * WW;
         const bool have = lane < kPer && mine < count;
         const float mp = have ? __ldcg(a.ws_m + (slot0 + mine) * RPB + row) : -INFINITY;
         const float lp = have ? __ldcg(a.ws_l + (slot0 + mine) * RPB + row) : 0.f;
@@ -217,7 +217,7 @@ __global__ void __launch_bounds__(kWideWarps * 32) merge_wide_kernel(const __gri
         const bool wide = Ev > 128;
 #pragma unroll
         for (int k = 0; k < kPer; ++k) {
-            const int p = min(p0 + k * kWideWarps, count - 1);
+            const int p = min(p0 + k * WW, count - 1);
             x[k] = lane * 4 < Ev ? __ldcg(reinterpret_cast<const float4*>(a.ws_o + ((slot0 + p) * RPB + row) * Ev + lane * 4))
                                  : make_float4(0.f, 0.f, 0.f, 0.f);
         }
@@ -243,7 +243,7 @@ __global__ void __launch_bounds__(kWideWarps * 32) merge_wide_kernel(const __gri
 #pragma unroll
         for (int k = 0; k < kPer; ++k) {
             const float wk = __shfl_sync(0xffffffffu, w, k);
-            const bool used = p0 + k * kWideWarps < count;   // a repeated last slot must not count twice
+            const bool used = p0 + k * WW < count;   // a repeated last slot must not count twice
             acc[0].x = fmaf(used ? x[k].x : 0.f, wk, acc[0].x);
             acc[0].y = fmaf(used ? x[k].y : 0.f, wk, acc[0].y);
             acc[0].z = fmaf(used ? x[k].z : 0.f, wk, acc[0].z);
@@ -252,7 +252,7 @@ __global__ void __launch_bounds__(kWideWarps * 32) merge_wide_kernel(const __gri
         if (wide) {                                         // columns 128 .. 255: a second pass over the same partials
 #pragma unroll 1
             for (int k = 0; k < kPer; ++k) {
-                const int p = p0 + k * kWideWarps;
+                const int p = p0 + k * WW;
                 if (p >= count) break;
                 const float wk = __shfl_sync(0xffffffffu, w, k);
                 if (128 + lane * 4 < Ev) {
@@ -276,12 +276,12 @@ __global__ void __launch_bounds__(kWideWarps * 32) merge_wide_kernel(const __gri
     if (warp < 2 && (warp * 128 + lane * 4) < Ev) {
         float Mx = sm_m[0];
 #pragma unroll
-        for (int k = 1; k < kWideWarps; ++k) Mx = fmaxf(Mx, sm_m[k]);
+        for (int k = 1; k < WW; ++k) Mx = fmaxf(Mx, sm_m[k]);
         const float mu = Mx == -INFINITY ? 0.f : Mx;
         float den = 0.f;
         float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for (int k = 0; k < kWideWarps; ++k) {
+        for (int k = 0; k < WW; ++k) {
             const float f = sm_m[k] == -INFINITY ? 0.f : exp2f(sm_m[k] - mu);      // a warp without partials holds zeros
             const float4 y = sm_o[k][warp * 32 + lane];
             den = fmaf(sm_l[k], f, den);

@@ -279,27 +279,9 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
             const int stage = it % C::NSTAGE;
             const uint32_t phase = (uint32_t)(it / C::NSTAGE) & 1u;
             if (!waited && (it >= C::NSTAGE || f >= a.stable_fragments)) {
-                if (f < a.stable_fragments && lane < 2) {
-                    // The ring is full.  Before waiting, ask for the rest of this CTA's stable tiles to be brought
-                    // into L2 (lane 0: keys, lane 1: values): HBM works while the preceding kernel finishes.
-                    int64_t u2 = u;
-                    int j2 = j, f2 = fscan;
-#pragma unroll 1
-                    for (int64_t t2 = t; t2 < t1 && t2 < t + 24; ++t2) {
-                        while (j2 >= pre[f2 + 1]) ++f2;
-                        if (f2 >= a.stable_fragments) break;
-                        const int tk = (j2 - pre[f2]) * C::TILE;
-                        const int nt = min(C::TILE, vis[f2] - tk);
-                        const unsigned char* src = static_cast<const unsigned char*>(lane ? a.ft.e[f2].v : a.ft.e[f2].k) +
-                                                   ((size_t)(u2 % a.Hkv) * a.ft.e[f2].rows + tk) * C::ROWB;
-                        bulk_prefetch_l2(src, (uint32_t)nt * C::ROWB);
-                        if (++j2 == TH) {
-                            j2 = 0;
-                            ++u2;
-                            f2 = 0;
-                        }
-                    }
-                }
+                // The ring is full, or the next tile belongs to a fragment the stream's earlier work may still write.
+                // (Asking for the CTA's further stable tiles to be brought into L2 here was measured and dropped: the
+                // prefetches queue in front of the query loads that follow the wait, +0.5 us per call.)
                 pdl_wait();                      // from here on: fragments that earlier work of the stream may have written
                 waited = true;
                 if (tid == 0) HOGATT_TRACE(a.debug_id, 5);
