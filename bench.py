@@ -396,6 +396,11 @@ def run_ours(args):
                 # the one head layout the reference's own CUDA kernel accepts: race it on the same GPU, same inputs
                 e["reference_cuda_kernel"] = race_reference_kernel(name, layers)
             extra[name] = e
+        if world == 1:
+            try:
+                extra["paged_gqa16"] = measure_paged(device)
+            except Exception as exc:                      # noqa: BLE001
+                extra["paged_gqa16"] = {"unavailable": str(exc)[:200]}
     us_per_call = secs / n_calls * 1e6
     value = bytes_per_call * n_calls / secs / 1e12
 
@@ -521,6 +526,51 @@ def measure_e2e(args, p: wl.Problem, device, dist, world):
                             "what": "KV cache resident on the device; only q/cos/sin/loc/lengths are copied in, output back to host"}}
 
 
+def measure_paged(device, name="paged_gqa16", copies=3, steps=20, warmup=5, race=True):
+    """The paged operator (``hogatt_paged_sdpa_launch``) at a decode shape: tensor-core kernel and CUDA-core kernel of
+    this library, and the reference's own paged kernel in a process of its own.  ``copies`` distinct caches are used
+    in turn (more than L2 in total), calls replayed from a CUDA graph, CUDA events around ``steps`` replays."""
+    from inference_lib_b200 import _cabi
+    pp = wl.paged_problem(name)
+    d = {k: (v.to(device) if torch.is_tensor(v) else v) for k, v in pp.items()}
+    caches = [(torch.roll(d["key_cache"], i, 2), torch.roll(d["value_cache"], i, 2)) for i in range(copies)]
+    out = torch.empty((d["queries"].shape[1], d["queries"].shape[2], d["queries"].shape[3], d["value_cache"].shape[3]),
+                      dtype=d["queries"].dtype, device=device)
+    res = {"bytes_per_call": pp["bytes"], "config": pp["meta"]}
+    hbm_peak, _ = measured_peak()
+    outs = {}
+    for label, kernel in (("tensor_core_kernel", _cabi.KERNEL_MMA), ("cuda_core_kernel", _cabi.KERNEL_FMA)):
+        bound = [_cabi.bind_paged(out=out, queries=d["queries"], locations=d["locations"], fragment_lengths=d["fragment_lengths"],
+                                  key_cache=kc, value_cache=vc, block_table=d["block_table"], scale=d["scale"], kernel=kernel)
+                 for kc, vc in caches]
+        stream = torch.cuda.Stream(device)
+        with torch.cuda.stream(stream):
+            for p, _ in bound:
+                assert _cabi.launch_paged(p, stream.cuda_stream) == 0
+            stream.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                for p, _ in bound:
+                    _cabi.launch_paged(p, torch.cuda.current_stream().cuda_stream)
+            for _ in range(warmup):
+                g.replay()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(steps):
+                g.replay()
+            e1.record()
+            stream.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (steps * copies)
+        res[label] = {"us_per_call": round(us, 2), "value_TBps": round(pp["bytes"] / us / 1e6, 4),
+                      "frac": round(pp["bytes"] / us / 1e3 / hbm_peak, 4)}
+        outs[label] = out.float().clone()
+    diff = (outs["tensor_core_kernel"] - outs["cuda_core_kernel"]).abs()
+    res["kernels_agree"] = {"max_abs": round(float(diff.max().item()), 6), "ok": bool(diff.max().item() <= 2e-2)}
+    if race:
+        res["reference_cuda_kernel"] = race_reference_kernel(name, copies)
+    return res
+
+
 # ------------------------------------------------------------------------------------------------
 # CPU legs (the only places that run the oracle)
 # ------------------------------------------------------------------------------------------------
@@ -632,7 +682,16 @@ def main():
     ap.add_argument("--no-rq", action="store_true", help="do not ask for the rotated-query side output")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     ap.add_argument("--no-isolated", action="store_true", help="skip the isolated cold-call leg (profiling runs)")
+    ap.add_argument("--paged-only", action="store_true",
+                    help="only the paged-operator leg (one GPU): prints its JSON object and exits (profiling runs)")
+    ap.add_argument("--no-reference-race", action="store_true", help="do not time the reference's own CUDA kernels")
     args = ap.parse_args()
+    if args.paged_only:
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device: the op has no CPU path")
+        print(json.dumps(measure_paged(torch.device("cuda:0"), steps=min(args.steps, 20), warmup=min(args.warmup, 5),
+                                       race=not args.no_reference_race)), flush=True)
+        return
     global KERNEL_CHOICE, LENGTH_SCALE, EMULATE_SHARD, HOST_PLAN, STABLE_FRAGMENTS
     HOST_PLAN = args.plan == "host"
     STABLE_FRAGMENTS = args.stable

@@ -282,6 +282,10 @@ typedef struct hogatt_paged_problem {
     const int32_t* cu_seqlens_q;   /* [W+1] or NULL */
     void*   workspace;             /* >= hogatt_paged_workspace_bytes(), 256-byte aligned */
     size_t  workspace_bytes;
+    int32_t kernel;                /* HOGATT_KERNEL_AUTO, _FMA (CUDA cores: any dtype and head size above) or _MMA
+                                      (mma.sync tensor cores: f16 / bf16 with E == Ev == 64 or 128; what AUTO takes
+                                      there unless HOGATT_PAGED_MMA=0 is set in the environment) */
+    int32_t reserved_;
 } hogatt_paged_problem;
 
 size_t hogatt_paged_workspace_bytes(const hogatt_paged_problem* p);

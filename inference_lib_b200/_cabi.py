@@ -44,7 +44,7 @@ class PagedProblem(C.Structure):
         ("dtype", C.c_int32), ("scale", C.c_float),
         ("out", C.c_void_p), ("queries", C.c_void_p), ("locations", C.c_void_p), ("fragment_lengths", C.c_void_p),
         ("key_cache", C.c_void_p), ("value_cache", C.c_void_p), ("block_table", C.c_void_p), ("cu_seqlens_q", C.c_void_p),
-        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("kernel", C.c_int32), ("reserved_", C.c_int32),
     ]
 
 
@@ -304,3 +304,46 @@ def append(*, keys, values, cosines, sines, write_to, key_fragments, value_fragm
     p.lengths_in, p.lengths_out = lengths_in.data_ptr(), lengths_out.data_ptr()
     p.device_status = status.data_ptr() if status is not None else None
     return int(load().hogatt_append_launch(C.byref(p), C.c_void_p(stream)))
+
+
+def bind_paged(*, out, queries, locations, fragment_lengths, key_cache, value_cache, block_table, scale,
+               cu_seqlens_q=None, kernel=KERNEL_AUTO):
+    """Fill a ``PagedProblem`` from torch CUDA tensors (fixed layout: ``queries [F,W,Hq,S,E]``, ``out [W,Hq,S,Ev]``;
+    packed layout with ``cu_seqlens_q``: ``queries [F,total_q,Hq,E]``, ``out [total_q,Hq,Ev]``) and give it a
+    workspace allocated with torch.  Returns ``(problem, keepalive)``; ``problem`` is ``None`` when the library
+    refuses the shape."""
+    import torch
+    p = PagedProblem()
+    packed = cu_seqlens_q is not None
+    if packed:
+        p.F, total_q, p.Hq, p.E = queries.shape
+        p.W, p.S, p.total_q_tokens = cu_seqlens_q.numel() - 1, 0, total_q
+    else:
+        p.F, p.W, p.Hq, p.S, p.E = queries.shape
+    p.Hkv, p.block_size, p.Ev = key_cache.shape[1], key_cache.shape[2], value_cache.shape[3]
+    p.max_blocks_per_seq = block_table.shape[1]
+    p.dtype, p.scale, p.kernel = dtype_code(out.dtype), float(scale), int(kernel)
+    p.out, p.queries, p.locations = out.data_ptr(), queries.data_ptr(), locations.data_ptr()
+    p.fragment_lengths, p.key_cache, p.value_cache = fragment_lengths.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr()
+    p.block_table = block_table.data_ptr()
+    p.cu_seqlens_q = cu_seqlens_q.data_ptr() if packed else None
+    need = int(load().hogatt_paged_workspace_bytes(C.byref(p)))
+    if need == 0:
+        return None, None
+    ws = torch.empty(need + 256, dtype=torch.uint8, device=out.device)
+    p.workspace, p.workspace_bytes = ws.data_ptr() + (-ws.data_ptr()) % 256, need
+    return p, [ws, out, queries, locations, fragment_lengths, key_cache, value_cache, block_table, cu_seqlens_q]
+
+
+def launch_paged(problem: PagedProblem, stream: int = 0) -> int:
+    """``hogatt_paged_sdpa_launch``: enqueue one call; returns the library's status code."""
+    return int(load().hogatt_paged_sdpa_launch(C.byref(problem), C.c_void_p(stream)))
+
+
+def paged_sdpa(*, stream: int = 0, **kw):
+    """:func:`bind_paged` + :func:`launch_paged`; returns ``(status, keepalive)`` -- keep the second alive until the
+    work has run."""
+    p, keep = bind_paged(**kw)
+    if p is None:
+        return -1, None
+    return launch_paged(p, stream), keep

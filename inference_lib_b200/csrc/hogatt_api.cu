@@ -770,7 +770,8 @@ int plan_paged(const hogatt_paged_problem* p, int sms, PagedPlan* pl) {
     if (units > (1 << 24)) return HOGATT_ERR_TOO_LARGE;
     pl->groups_bound = (int)groups;
     pl->units = (int)std::max<int64_t>(units, 1);
-    pl->splits = std::max(1, std::min(32, (2 * sms + pl->units - 1) / pl->units));
+    static const int per_sm = [] { const char* e = getenv("HOGATT_PAGED_CTAS"); return e ? atoi(e) : 2; }();
+    pl->splits = std::max(1, std::min(32, (per_sm * sms + pl->units - 1) / pl->units));
     const size_t slots = (size_t)pl->units * pl->splits * kFmaRows;
     pl->o = 0;
     pl->m = pl->o + align_up(slots * p->Ev * sizeof(float), 256);
@@ -793,8 +794,53 @@ int launch_paged(const PagedArgs& a, const PagedPlan& pl, int dev, int smem_opti
     return HOGATT_OK;
 }
 
+// HOGATT_PAGED_MMA=0 in the environment keeps AUTO on the CUDA-core paged kernel (A/B measurements).
+bool paged_mma_disabled() {
+    static const bool off = [] {
+        const char* v = getenv("HOGATT_PAGED_MMA");
+        return v && v[0] == '0';
+    }();
+    return off;
+}
+
+template <class T, int HD, int NS>
+int launch_paged_mma_ns(const PagedArgs& a, const PagedPlan& pl, int dev, int smem_optin, cudaStream_t stream) {
+    static std::atomic<size_t> granted[kMaxDevices];
+    const size_t smem = paged_mma_smem_bytes<HD, NS>(a.F);
+    if (smem > (size_t)smem_optin) return HOGATT_ERR_TOO_MANY_FRAGMENTS;
+    int rc = ensure_smem_limit(paged_mma_kernel<T, HD, NS>, dev, smem, granted);
+    if (rc != HOGATT_OK) return rc;
+    paged_mma_kernel<T, HD, NS><<<dim3(pl.units, pl.splits), PagedMmaCfg<HD, NS>::THREADS, smem, stream>>>(a);
+    HOGATT_CUDA_OK(cudaGetLastError());
+    return HOGATT_OK;
+}
+
+template <class T, int HD>
+int launch_paged_mma(const PagedArgs& a, const PagedPlan& pl, int dev, int smem_optin, cudaStream_t stream) {
+    static const int ns = [] { const char* e = getenv("HOGATT_PAGED_STAGES"); return e ? atoi(e) : 2; }();
+    int rc = ns == 3 ? launch_paged_mma_ns<T, HD, 3>(a, pl, dev, smem_optin, stream)
+           : ns == 4 ? launch_paged_mma_ns<T, HD, 4>(a, pl, dev, smem_optin, stream)
+                     : launch_paged_mma_ns<T, HD, 2>(a, pl, dev, smem_optin, stream);
+    if (rc != HOGATT_OK) return rc;
+    paged_merge_kernel<T><<<pl.units, kMergeWarps * 32, 0, stream>>>(a);
+    HOGATT_CUDA_OK(cudaGetLastError());
+    return HOGATT_OK;
+}
+
 template <class T>
-int launch_paged_dims(const PagedArgs& a, const PagedPlan& pl, int dev, int smem_optin, cudaStream_t stream) {
+bool paged_mma_eligible(const PagedArgs& a) {
+    return !std::is_same<T, float>::value && a.E == a.Ev && (a.E == 64 || a.E == 128);
+}
+
+template <class T>
+int launch_paged_dims(const PagedArgs& a, const PagedPlan& pl, int kernel, int dev, int smem_optin, cudaStream_t stream) {
+    if (kernel != HOGATT_KERNEL_AUTO && kernel != HOGATT_KERNEL_FMA && kernel != HOGATT_KERNEL_MMA) return HOGATT_ERR_BAD_KERNEL_CHOICE;
+    if (kernel == HOGATT_KERNEL_MMA && !paged_mma_eligible<T>(a)) return HOGATT_ERR_BAD_KERNEL_CHOICE;
+    if constexpr (!std::is_same<T, float>::value) {
+        if (kernel == HOGATT_KERNEL_MMA || (kernel == HOGATT_KERNEL_AUTO && paged_mma_eligible<T>(a) && !paged_mma_disabled()))
+            return a.E == 128 ? launch_paged_mma<T, 128>(a, pl, dev, smem_optin, stream)
+                              : launch_paged_mma<T, 64>(a, pl, dev, smem_optin, stream);
+    }
     switch (a.Ev) {
         case 32: return launch_paged<T, 32>(a, pl, dev, smem_optin, stream);
         case 64: return launch_paged<T, 64>(a, pl, dev, smem_optin, stream);
@@ -938,9 +984,9 @@ int hogatt_paged_sdpa_launch(const hogatt_paged_problem* p, hogatt_stream_t stre
     a.ws_m = reinterpret_cast<float*>(ws + pl.m);
     a.ws_l = reinterpret_cast<float*>(ws + pl.l);
     switch (p->dtype) {
-        case HOGATT_F32: return launch_paged_dims<float>(a, pl, dev, smem_optin, stream);
-        case HOGATT_F16: return launch_paged_dims<__half>(a, pl, dev, smem_optin, stream);
-        case HOGATT_BF16: return launch_paged_dims<__nv_bfloat16>(a, pl, dev, smem_optin, stream);
+        case HOGATT_F32: return launch_paged_dims<float>(a, pl, p->kernel, dev, smem_optin, stream);
+        case HOGATT_F16: return launch_paged_dims<__half>(a, pl, p->kernel, dev, smem_optin, stream);
+        case HOGATT_BF16: return launch_paged_dims<__nv_bfloat16>(a, pl, p->kernel, dev, smem_optin, stream);
     }
     return HOGATT_ERR_UNSUPPORTED_DTYPE;
 }

@@ -258,3 +258,32 @@ EDGE_CASES: Dict[str, Dict] = {
 
 def edge_problem(name: str, seed: int = 1234) -> Problem:
     return make_problem(name, seed=seed, **EDGE_CASES[name])
+
+
+# ---- paged decode (operators hogwild_paged_sdpa / copy_to_blocks) -------------------------------------------------
+PAGED_CONFIGS = {
+    # 8 sequences of 16,384 keys in 16-row blocks, 32 query / 2 kv heads of size 128 (the head layout the reference's
+    # paged kernel is instantiated for, src/kernels/kernel_v21.cuh:1025), one token per sequence and step
+    "paged_gqa16": dict(W=8, Hq=32, Hkv=2, E=128, S=1, F=1, block_size=16, length=16384, dtype=torch.bfloat16),
+}
+
+
+def paged_problem(name: str = "paged_gqa16", seed: int = 0) -> dict:
+    """Seeded inputs of a paged decode call: ``queries [F,W,Hq,S,E]`` (already rotated), ``locations [F,W,S]``,
+    ``fragment_lengths [F]``, ``key_cache`` / ``value_cache [blocks,Hkv,block_size,E]``, ``block_table [W,max_blocks]``
+    (a random permutation of the blocks), ``scale``; ``bytes`` = every visible key and value once, queries, output."""
+    c = PAGED_CONFIGS[name]
+    g = torch.Generator().manual_seed(1000 + seed)
+    W, Hq, Hkv, E, S, F, bs, L, dtype = (c[k] for k in ("W", "Hq", "Hkv", "E", "S", "F", "block_size", "length", "dtype"))
+    max_blocks = (L + bs - 1) // bs
+    nblk = W * max_blocks
+    kc = torch.randn(nblk, Hkv, bs, E, generator=g).to(dtype)
+    vc = torch.randn(nblk, Hkv, bs, E, generator=g).to(dtype)
+    table = torch.randperm(nblk, generator=g).to(torch.int32).reshape(W, max_blocks).contiguous()
+    rq = torch.randn(F, W, Hq, S, E, generator=g).to(dtype)
+    loc = torch.full((F, W, S), L - 1, dtype=torch.int32)
+    lens = torch.full((F,), L, dtype=torch.int32)
+    esz = 2 if dtype != torch.float32 else 4
+    nbytes = W * Hkv * L * 2 * E * esz + rq.numel() * esz + W * Hq * S * E * esz
+    return dict(name=name, queries=rq, locations=loc, fragment_lengths=lens, key_cache=kc, value_cache=vc, block_table=table,
+                scale=E ** -0.5, bytes=nbytes, meta=dict(c, dtype=str(dtype).replace("torch.", "")))

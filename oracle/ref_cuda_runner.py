@@ -111,6 +111,8 @@ def run_timing(args):
     from inference_lib_b200 import workloads as wl
     ops = load()
     dev = torch.device("cuda:0")
+    if args.workload in wl.PAGED_CONFIGS:
+        return run_paged_timing(args, ops, dev, wl)
     p = wl.baseline_problem(args.workload)
     _check_heads(p.Hq, p.Hkv, p.E, p.Ev)
     d = p.to(dev)
@@ -138,6 +140,37 @@ def run_timing(args):
                       "us_per_call": round(us, 3), "value_TBps": round(p.algorithmic_bytes() / us / 1e6, 4),
                       "layers_per_step": args.layers, "steps": args.steps, "launch": "eager, default stream (the reference "
                       "copies a pointer table from host memory in every call and cannot be captured into a graph)"}), flush=True)
+
+
+def run_paged_timing(args, ops, dev, wl):
+    """``hogwild_paged_sdpa`` of the reference on a paged decode workload; ``--layers`` distinct caches in turn."""
+    pp = wl.paged_problem(args.workload)
+    rq, kc, vc, table = pp["queries"], pp["key_cache"], pp["value_cache"], pp["block_table"]
+    F, W, Hq, S, E = rq.shape
+    _check_heads(Hq, kc.shape[1], E, vc.shape[3])
+    _check_paged(pp["locations"], pp["fragment_lengths"], kc, vc, table, W)
+    d = {k: (v.to(dev).contiguous() if torch.is_tensor(v) else v) for k, v in pp.items()}
+    caches = [(torch.roll(d["key_cache"], i, 2), torch.roll(d["value_cache"], i, 2)) for i in range(args.layers)]
+    out = torch.zeros((W, Hq, S, vc.shape[3]), dtype=rq.dtype, device=dev)
+
+    def step():
+        for k, v in caches:
+            ops.hogwild_paged_sdpa(out, float(pp["scale"]), d["locations"], d["queries"], d["fragment_lengths"], k, v,
+                                   d["block_table"])
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / (args.steps * args.layers)
+    print(json.dumps({"impl": "reference CUDA paged kernel (kernel_v21, recompiled for sm_100a)", "workload": args.workload,
+                      "us_per_call": round(us, 3), "value_TBps": round(pp["bytes"] / us / 1e6, 4),
+                      "caches_in_turn": args.layers, "steps": args.steps, "launch": "eager, default stream"}), flush=True)
 
 
 def main():

@@ -108,3 +108,91 @@ def test_append_then_attend_round_trip(A):
     ck, cv = oracle.copy_to_blocks(ks, vs, kc.clone(), vc.clone(), table, seq)
     ref = oracle.paged_sdpa(rq, loc, lens, ck, cv, table, E ** -0.5)
     check_against(out, ref.numpy(), dtype)
+
+
+# ---- the tensor-core paged kernel by name, against the CUDA-core one and the oracle ---------------------------------
+MMA_CASES = [
+    # dtype, W, S, Hkv, G, E, bs, F, max_len
+    (torch.bfloat16, 3, 1, 2, 16, 128, 16, 2, 1500),      # decode, 16 heads per kv head: one m-tile of heads
+    (torch.bfloat16, 2, 3, 2, 4, 128, 24, 3, 700),        # block size that is no multiple of the copy group; 3 tokens x 4 heads
+    (torch.float16, 2, 2, 1, 40, 64, 8, 2, 333),          # head size 64, 40 heads per kv head (three head blocks)
+    (torch.bfloat16, 5, 1, 1, 8, 128, 256, 1, 2100),      # large blocks
+]
+
+
+def _run_paged(kernel, rq, loc, lens, kc, vc, table, scale, cu=None):
+    from inference_lib_b200 import _cabi
+    d = lambda t: t.to(DEV).contiguous()
+    if cu is None:
+        out = torch.full((rq.shape[1], rq.shape[2], rq.shape[3], vc.shape[3]), float("nan"), dtype=rq.dtype, device=DEV)
+    else:
+        out = torch.full((rq.shape[1], rq.shape[2], vc.shape[3]), float("nan"), dtype=rq.dtype, device=DEV)
+    keep = [d(rq), d(loc), d(lens), d(kc), d(vc), d(table)] + ([d(cu)] if cu is not None else [])
+    rc, ws = _cabi.paged_sdpa(out=out, queries=keep[0], locations=keep[1], fragment_lengths=keep[2], key_cache=keep[3],
+                              value_cache=keep[4], block_table=keep[5], scale=scale,
+                              cu_seqlens_q=keep[6] if cu is not None else None, kernel=kernel,
+                              stream=torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    return rc, out
+
+
+@pytest.mark.parametrize("case", MMA_CASES, ids=[str(i) for i in range(len(MMA_CASES))])
+def test_tensor_core_paged_kernel_matches_oracle_and_cuda_core_kernel(case):
+    from inference_lib_b200 import _cabi
+    dtype, W, S, Hkv, G, E, bs, F, max_len = case
+    rng = np.random.default_rng(sum(case[1:]))
+    Hq = Hkv * G
+    lens = torch.tensor([max_len] + [int(rng.integers(1, max_len)) for _ in range(F - 1)], dtype=torch.int32)
+    kc, vc, table, g = _caches(rng, W, Hkv, bs, E, E, max_len, dtype)
+    rq = torch.randn(F, W, Hq, S, E, generator=g).to(dtype)
+    loc = torch.from_numpy(rng.integers(-1, max_len + 20, size=(F, W, S)).astype(np.int32))
+    loc[0, :, :] = torch.clamp(loc[0], min=0)
+    # whatever lies in a block past a sequence's visible rows must never reach a result
+    last = (max_len - 1) // bs
+    if (max_len % bs) != 0:
+        for w in range(W):
+            kc[table[w, last], :, max_len % bs:] = float("nan")
+            vc[table[w, last], :, max_len % bs:] = float("inf")
+    ref = oracle.paged_sdpa(rq, loc, lens, kc.nan_to_num(0.0, 0.0, 0.0), vc.nan_to_num(0.0, 0.0, 0.0), table, E ** -0.5)
+    rc_m, out_m = _run_paged(_cabi.KERNEL_MMA, rq, loc, lens, kc, vc, table, E ** -0.5)
+    rc_f, out_f = _run_paged(_cabi.KERNEL_FMA, rq, loc, lens, kc, vc, table, E ** -0.5)
+    rc_a, out_a = _run_paged(_cabi.KERNEL_AUTO, rq, loc, lens, kc, vc, table, E ** -0.5)
+    assert (rc_m, rc_f, rc_a) == (0, 0, 0)
+    check_against(out_m, ref.numpy(), dtype, what=f"tensor-core paged kernel {case}")
+    check_against(out_f, ref.numpy(), dtype, what=f"CUDA-core paged kernel {case}")
+    assert torch.equal(out_a, out_m), "AUTO takes the tensor-core kernel for 16-bit types with equal head sizes of 64 / 128"
+
+
+def test_tensor_core_paged_kernel_packed_layout():
+    from inference_lib_b200 import _cabi
+    dtype, G, E, bs, seqs = torch.bfloat16, 8, 128, 16, [3, 0, 5, 1, 2]
+    rng = np.random.default_rng(77)
+    W, Hkv, F = len(seqs), 2, 2
+    Hq = Hkv * G
+    cu = torch.tensor([0] + list(np.cumsum(seqs)), dtype=torch.int32)
+    total_q = int(cu[-1])
+    lens = torch.from_numpy(rng.integers(1, 900, size=(F, W)).astype(np.int32))
+    kc, vc, table, g = _caches(rng, W, Hkv, bs, E, E, int(lens.max()), dtype)
+    rq = torch.randn(F, total_q, Hq, E, generator=g).to(dtype)
+    loc = torch.from_numpy(rng.integers(-1, 950, size=(F, total_q)).astype(np.int32))
+    loc[0] = torch.clamp(loc[0], min=0)
+    ref = oracle.varlen_paged_sdpa(rq, loc, lens, kc, vc, table, cu, E ** -0.5)
+    for kernel in (_cabi.KERNEL_MMA, _cabi.KERNEL_FMA):
+        rc, out = _run_paged(kernel, rq, loc, lens, kc, vc, table, E ** -0.5, cu=cu)
+        assert rc == 0
+        check_against(out, ref.numpy(), dtype, what=f"packed layout, kernel {kernel}")
+
+
+def test_tensor_core_paged_kernel_is_refused_where_it_cannot_run():
+    from inference_lib_b200 import _cabi
+    rng = np.random.default_rng(5)
+    for dtype, E, Ev in ((torch.float32, 64, 64), (torch.bfloat16, 128, 64), (torch.float16, 32, 32)):
+        kc, vc, table, g = _caches(rng, 2, 2, 16, E, Ev, 40, dtype)
+        rq = torch.randn(1, 2, 4, 1, E, generator=g).to(dtype)
+        loc = torch.full((1, 2, 1), 30, dtype=torch.int32)
+        lens = torch.tensor([35], dtype=torch.int32)
+        rc, out = _run_paged(_cabi.KERNEL_MMA, rq, loc, lens, kc, vc, table, 0.1)
+        assert rc == -9
+        assert torch.isnan(out).all()                    # nothing ran
+        rc, out = _run_paged(_cabi.KERNEL_AUTO, rq, loc, lens, kc, vc, table, 0.1)
+        assert rc == 0 and torch.isfinite(out).all()
