@@ -770,8 +770,7 @@ int plan_paged(const hogatt_paged_problem* p, int sms, PagedPlan* pl) {
     if (units > (1 << 24)) return HOGATT_ERR_TOO_LARGE;
     pl->groups_bound = (int)groups;
     pl->units = (int)std::max<int64_t>(units, 1);
-    static const int per_sm = [] { const char* e = getenv("HOGATT_PAGED_CTAS"); return e ? atoi(e) : 2; }();
-    pl->splits = std::max(1, std::min(32, (per_sm * sms + pl->units - 1) / pl->units));
+    pl->splits = std::max(1, std::min(32, (2 * sms + pl->units - 1) / pl->units));
     const size_t slots = (size_t)pl->units * pl->splits * kFmaRows;
     pl->o = 0;
     pl->m = pl->o + align_up(slots * p->Ev * sizeof(float), 256);
@@ -803,25 +802,17 @@ bool paged_mma_disabled() {
     return off;
 }
 
-template <class T, int HD, int NS>
-int launch_paged_mma_ns(const PagedArgs& a, const PagedPlan& pl, int dev, int smem_optin, cudaStream_t stream) {
-    static std::atomic<size_t> granted[kMaxDevices];
-    const size_t smem = paged_mma_smem_bytes<HD, NS>(a.F);
-    if (smem > (size_t)smem_optin) return HOGATT_ERR_TOO_MANY_FRAGMENTS;
-    int rc = ensure_smem_limit(paged_mma_kernel<T, HD, NS>, dev, smem, granted);
-    if (rc != HOGATT_OK) return rc;
-    paged_mma_kernel<T, HD, NS><<<dim3(pl.units, pl.splits), PagedMmaCfg<HD, NS>::THREADS, smem, stream>>>(a);
-    HOGATT_CUDA_OK(cudaGetLastError());
-    return HOGATT_OK;
-}
-
+// Two ring stages and two CTAs per SM: measured best at 8 sequences x 16 K keys (deeper rings cost resident CTAs:
+// three stages 53 us against 40; three CTAs' worth of splits per SM 51 us).
 template <class T, int HD>
 int launch_paged_mma(const PagedArgs& a, const PagedPlan& pl, int dev, int smem_optin, cudaStream_t stream) {
-    static const int ns = [] { const char* e = getenv("HOGATT_PAGED_STAGES"); return e ? atoi(e) : 2; }();
-    int rc = ns == 3 ? launch_paged_mma_ns<T, HD, 3>(a, pl, dev, smem_optin, stream)
-           : ns == 4 ? launch_paged_mma_ns<T, HD, 4>(a, pl, dev, smem_optin, stream)
-                     : launch_paged_mma_ns<T, HD, 2>(a, pl, dev, smem_optin, stream);
+    static std::atomic<size_t> granted[kMaxDevices];
+    const size_t smem = paged_mma_smem_bytes<HD>(a.F);
+    if (smem > (size_t)smem_optin) return HOGATT_ERR_TOO_MANY_FRAGMENTS;
+    int rc = ensure_smem_limit(paged_mma_kernel<T, HD>, dev, smem, granted);
     if (rc != HOGATT_OK) return rc;
+    paged_mma_kernel<T, HD><<<dim3(pl.units, pl.splits), PagedMmaCfg<HD>::THREADS, smem, stream>>>(a);
+    HOGATT_CUDA_OK(cudaGetLastError());
     paged_merge_kernel<T><<<pl.units, kMergeWarps * 32, 0, stream>>>(a);
     HOGATT_CUDA_OK(cudaGetLastError());
     return HOGATT_OK;

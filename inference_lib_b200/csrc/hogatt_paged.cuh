@@ -269,19 +269,30 @@ __global__ void __launch_bounds__(PagedMmaCfg<HD, NS>::THREADS) paged_mma_kernel
     const int T_u = pre[a.F];
     const int t0 = (int)((int64_t)split * T_u / a.splits), t1 = (int)((int64_t)(split + 1) * T_u / a.splits);
 
-    // one tile's rows into a stage: thread i takes chunk i % CPR of row i / CPR, keys first, then values
+    // One tile's rows into a stage.  The copies are dealt as pass k = 0 .. NP-1 of RP rows, a thread takes chunk
+    // lane % CPR of row (tid / CPR) + k * RP; a warp therefore touches 16 distinct rows of the tile, and lane j < 16
+    // looks up row j's place in the cache (one division and one block-table load per thread and tile) for the others.
     auto fetch = [&](int t, int stage, int fhint) {
+        constexpr int RP = C::THREADS / CPR, NP = C::TILE / RP, RW = 32 / CPR;
         int f = fhint;
         while (t >= pre[f + 1]) ++f;
         const int tok0 = (t - pre[f]) * C::TILE;
         const int ntok = min(C::TILE, vis[f] - tok0);
         const uint32_t base = smem_u32(stages + stage * C::STAGE_BYTES);
-#pragma unroll 4
-        for (int i = tid; i < C::TILE * CPR; i += C::THREADS) {
-            const int tok = i / CPR, c = i - tok * CPR;
+        long long mine = 0;
+        {
+            const int j = lane & 15;
+            const int tok = warp * RW + (j % RW) + (j / RW) * RP;
+            const int l = tok0 + (tok < ntok ? tok : 0);
+            const int blk = l / a.block_size;
+            mine = ((long long)table[blk] * a.Hkv + u.hkv) * a.block_size + (l - blk * a.block_size);
+        }
+        const int c = lane % CPR, sub = lane / CPR;
+#pragma unroll
+        for (int k = 0; k < NP; ++k) {
+            const long long row = __shfl_sync(0xffffffffu, mine, k * RW + sub);
+            const int tok = warp * RW + sub + k * RP;
             const bool real = tok < ntok;
-            const int l = tok0 + (real ? tok : 0);
-            const size_t row = ((size_t)table[l / a.block_size] * a.Hkv + u.hkv) * a.block_size + l % a.block_size;
             cp_async_16(base + tok * C::PITCH + c * 16, kc + row * HD + c * 8, real);
             cp_async_16(base + C::KV_BYTES + tok * C::PITCH + c * 16, vc + row * HD + c * 8, real);
         }
@@ -304,9 +315,13 @@ __global__ void __launch_bounds__(PagedMmaCfg<HD, NS>::THREADS) paged_mma_kernel
     for (int t = t0, it = 0; t < t1; ++t, ++it) {
         while (t >= pre[fscan + 1]) ++fscan;
         const int f = fscan;
+        cp_async_wait<C::NSTAGE - 2>();                             // this thread's copies of tile t have landed
+        __syncthreads();                                            // everyone's have, and everyone has left tile t - 1
+        if (t + C::NSTAGE - 1 < t1) fetch(t + C::NSTAGE - 1, (it + C::NSTAGE - 1) % C::NSTAGE, fscan);   // into tile t - 1's stage
+        else cp_async_commit();
         if (f != cur_f) {
-            // this fragment's query rows (already rotated) and their limits; everyone left the previous tile at the
-            // barrier that ends an iteration, so the query tile is free
+            // this fragment's query rows (already rotated) and their limits; the query tile is only read right after
+            // it is written (the A fragments stay in registers), and a barrier has passed since
             cur_f = f;
             for (int i = tid; i < kFmaRows * CPR; i += C::THREADS) {
                 const int r = i / CPR, c = i - r * CPR;
@@ -332,10 +347,6 @@ __global__ void __launch_bounds__(PagedMmaCfg<HD, NS>::THREADS) paged_mma_kernel
             lim0 = lim_s[lane >> 2];
             lim1 = lim_s[(lane >> 2) + 8];
         }
-        if (t + C::NSTAGE - 1 < t1) fetch(t + C::NSTAGE - 1, (it + C::NSTAGE - 1) % C::NSTAGE, fscan);
-        else cp_async_commit();
-        cp_async_wait<C::NSTAGE - 1>();                             // all but the newest NSTAGE - 1 groups: tile t has landed
-        __syncthreads();                                            // ... for every warp
 
         const int tok0 = (t - pre[f]) * C::TILE;
         const uint32_t sk = smem_u32(stages + (it % C::NSTAGE) * C::STAGE_BYTES), sv = sk + C::KV_BYTES;
@@ -373,6 +384,8 @@ __global__ void __launch_bounds__(PagedMmaCfg<HD, NS>::THREADS) paged_mma_kernel
         const float al0 = exp2f(m0 - mu0), al1 = exp2f(m1 - mu1);   // (-inf -> 0)
         m0 = n0;
         m1 = n1;
+        // a row's maximum settles after a few tiles: the accumulators are rescaled only when some row's has grown
+        const bool grew = __any_sync(0xffffffffu, al0 != 1.f || al1 != 1.f);
         float ps0 = 0.f, ps1 = 0.f;
 #pragma unroll
         for (int j = 0; j < 2; ++j)
@@ -396,14 +409,16 @@ __global__ void __launch_bounds__(PagedMmaCfg<HD, NS>::THREADS) paged_mma_kernel
             for (int n = 0; n < NT_O; n += 2) {
                 uint32_t b0, b1, b2, b3;
                 ldmatrix_x4_trans(vaddr + n * 16, b0, b1, b2, b3);
-                o[n][0] *= al0; o[n][1] *= al0; o[n][2] *= al1; o[n][3] *= al1;
-                o[n + 1][0] *= al0; o[n + 1][1] *= al0; o[n + 1][2] *= al1; o[n + 1][3] *= al1;
+                if (grew) {
+                    o[n][0] *= al0; o[n][1] *= al0; o[n][2] *= al1; o[n][3] *= al1;
+                    o[n + 1][0] *= al0; o[n + 1][1] *= al0; o[n + 1][2] *= al1; o[n + 1][3] *= al1;
+                }
                 mma_16816<T>(o[n], pa, b0, b1);
                 mma_16816<T>(o[n + 1], pa, b2, b3);
             }
         }
-        __syncthreads();                                            // the stage may be refilled, the query tile rewritten
     }
+    __syncthreads();                                                // every warp has left the last tile: the ring is free
 
     // ---- fold the four warps' results into the split's partial -------------------------------------------------
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
