@@ -770,7 +770,10 @@ int plan_paged(const hogatt_paged_problem* p, int sms, PagedPlan* pl) {
     if (units > (1 << 24)) return HOGATT_ERR_TOO_LARGE;
     pl->groups_bound = (int)groups;
     pl->units = (int)std::max<int64_t>(units, 1);
-    pl->splits = std::max(1, std::min(32, (2 * sms + pl->units - 1) / pl->units));
+    // at most 24 partials per row: what the merge step fetches in one round trip
+    // and CTAs for three per SM (what registers and shared memory of the tensor-core kernel allow; measured 36.7 us
+    // with two per SM, 34.7 with three, at 8 sequences x 16 K keys)
+    pl->splits = std::max(1, std::min(24, (3 * sms + pl->units - 1) / pl->units));
     const size_t slots = (size_t)pl->units * pl->splits * kFmaRows;
     pl->o = 0;
     pl->m = pl->o + align_up(slots * p->Ev * sizeof(float), 256);
@@ -788,7 +791,7 @@ int launch_paged(const PagedArgs& a, const PagedPlan& pl, int dev, int smem_opti
     if (rc != HOGATT_OK) return rc;
     paged_attention_kernel<T, EV><<<dim3(pl.units, pl.splits), kFmaThreads, smem, stream>>>(a);
     HOGATT_CUDA_OK(cudaGetLastError());
-    paged_merge_kernel<T><<<pl.units, kMergeWarps * 32, 0, stream>>>(a);
+    paged_merge_kernel<T><<<dim3(pl.units, kFmaRows / kMergeWarps), kMergeWarps * 32, 0, stream>>>(a);
     HOGATT_CUDA_OK(cudaGetLastError());
     return HOGATT_OK;
 }
@@ -802,8 +805,8 @@ bool paged_mma_disabled() {
     return off;
 }
 
-// Two ring stages and two CTAs per SM: measured best at 8 sequences x 16 K keys (deeper rings cost resident CTAs:
-// three stages 53 us against 40; three CTAs' worth of splits per SM 51 us).
+// Two ring stages: measured best at 8 sequences x 16 K keys (deeper rings cost resident CTAs: three stages 53 us
+// against 40).
 template <class T, int HD>
 int launch_paged_mma(const PagedArgs& a, const PagedPlan& pl, int dev, int smem_optin, cudaStream_t stream) {
     static std::atomic<size_t> granted[kMaxDevices];
@@ -811,10 +814,8 @@ int launch_paged_mma(const PagedArgs& a, const PagedPlan& pl, int dev, int smem_
     if (smem > (size_t)smem_optin) return HOGATT_ERR_TOO_MANY_FRAGMENTS;
     int rc = ensure_smem_limit(paged_mma_kernel<T, HD>, dev, smem, granted);
     if (rc != HOGATT_OK) return rc;
-    paged_mma_kernel<T, HD><<<dim3(pl.units, pl.splits), PagedMmaCfg<HD>::THREADS, smem, stream>>>(a);
-    HOGATT_CUDA_OK(cudaGetLastError());
-    paged_merge_kernel<T><<<pl.units, kMergeWarps * 32, 0, stream>>>(a);
-    HOGATT_CUDA_OK(cudaGetLastError());
+    HOGATT_CUDA_OK(launch_kernel(paged_mma_kernel<T, HD>, dim3(pl.units, pl.splits), dim3(PagedMmaCfg<HD>::THREADS), smem, stream, a));
+    HOGATT_CUDA_OK(launch_kernel(paged_merge_kernel<T>, dim3(pl.units, kFmaRows / kMergeWarps), dim3(kMergeWarps * 32), 0, stream, a));
     return HOGATT_OK;
 }
 

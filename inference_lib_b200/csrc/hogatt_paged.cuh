@@ -236,6 +236,10 @@ __global__ void __launch_bounds__(PagedMmaCfg<HD, NS>::THREADS) paged_mma_kernel
     int* vis = reinterpret_cast<int*>(smem_raw + C::OFF_PLAN);
     int* pre = vis + a.F;
 
+    // Launched with programmatic stream serialization: wait for the stream's earlier work before anything is read,
+    // then let the merge kernel take its place on the SMs (it waits for this whole grid itself).
+    pdl_wait();
+    pdl_trigger();
     PagedUnit u;
     if (!locate_paged_unit(a, blockIdx.x, &u)) return;            // (uniform over the CTA)
     const int split = blockIdx.y;
@@ -473,10 +477,12 @@ __global__ void __launch_bounds__(PagedMmaCfg<HD, NS>::THREADS) paged_mma_kernel
 template <class T>
 __global__ void __launch_bounds__(kMergeWarps * 32) paged_merge_kernel(const __grid_constant__ PagedArgs a) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    pdl_wait();                                                    // (returns at once after an ordinary launch)
     PagedUnit u;
     if (!locate_paged_unit(a, blockIdx.x, &u)) return;
     T* const out = static_cast<T*>(a.out);
-    for (int row = warp; row < kFmaRows; row += kMergeWarps) {
+    // grid (units, row groups): one warp per output row where the grid allows, so that a row's partials are one round trip
+    for (int row = blockIdx.y * kMergeWarps + warp; row < kFmaRows; row += gridDim.y * kMergeWarps) {
         int s_abs, hq;
         if (!paged_row(a, u, row, &s_abs, &hq)) continue;
         const int splits = a.splits;
