@@ -739,7 +739,7 @@ int attention_launch(const hogatt_problem* p, bool fused, cudaStream_t stream, c
     memset(&pf, 0, sizeof(pf));
     for (int i = 0; i < peers->world; ++i) pf.f[i] = peers->flags[i];
     HOGATT_CUDA_OK(launch_kernel(gather_signal_kernel, dim3(1), dim3(32), 0, stream, pf, (int)peers->world, (int)peers->rank,
-                                 p->device_status));
+                                 p->device_status, (int)args.debug_id));
     return HOGATT_OK;
 }
 
@@ -1054,6 +1054,10 @@ int hogatt_debug_trace(unsigned long long* out, unsigned long long* mout, int re
         }
         HOGATT_CUDA_OK(cudaMemcpyToSymbol(g_mtrace, init, sizeof(init)));
     }
+    return HOGATT_OK;
+}
+int hogatt_debug_strace(unsigned long long* out) {
+    HOGATT_CUDA_OK(cudaMemcpyFromSymbol(out, g_strace, sizeof(g_strace)));
     return HOGATT_OK;
 }
 int hogatt_debug_spans(unsigned long long* out8, int reset) {

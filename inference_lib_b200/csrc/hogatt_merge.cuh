@@ -6,6 +6,19 @@ namespace hogatt {
 
 constexpr int kMergeWarps = 4;
 
+// Four consecutive output values as ONE store (8 bytes of 16-bit values, 16 bytes of fp32).  `dst` is aligned to
+// that: outputs are 16-byte aligned, rows are Ev values long and a lane's first column is a multiple of four.  Over
+// NVLink (the output rows of a sharded call go to every peer) four 2-byte stores per lane were four partial-sector
+// writes per 8 bytes.
+template <class T>
+__device__ __forceinline__ void store4(T* dst, float a, float b, float c, float d) {
+    if constexpr (sizeof(T) == 2) {
+        *reinterpret_cast<uint2*>(dst) = make_uint2(pack2<T>(a, b), pack2<T>(c, d));
+    } else {
+        *reinterpret_cast<float4*>(dst) = make_float4(a, b, c, d);
+    }
+}
+
 // Combine the partial results of one output row (one warp), normalise, round to the storage type.
 //   out = sum_p O_p * 2^(m_p - M) / sum_p l_p * 2^(m_p - M),   M = max_p m_p
 // A row no key was visible to (every m_p = -inf, or no partial at all) comes out as zeros.
@@ -115,15 +128,8 @@ __device__ __forceinline__ void merge_partials_rows(const float* __restrict__ ws
         }
         if (blind) acc = make_float4(0.f, 0.f, 0.f, 0.f);
         if (mine) {
-            const T r0 = Scalar<T>::from_float(acc.x * inv), r1 = Scalar<T>::from_float(acc.y * inv);
-            const T r2 = Scalar<T>::from_float(acc.z * inv), r3 = Scalar<T>::from_float(acc.w * inv);
-            for (int b = 0; b < nbases; ++b) {          // one destination, or the full-size output of every rank
-                T* dst = bases[b] + offset + e;
-                dst[0] = r0;
-                dst[1] = r1;
-                dst[2] = r2;
-                dst[3] = r3;
-            }
+            for (int b = 0; b < nbases; ++b)            // one destination, or the full-size output of every rank
+                store4<T>(bases[b] + offset + e, acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv);
         }
     }
 }
@@ -143,7 +149,6 @@ __global__ void __launch_bounds__(MW * 32) merge_kernel(const __grid_constant__ 
     if (threadIdx.x == 0) atomicMin(&g_mtrace[a.debug_id % kTraceCalls][0], global_timer_ns_());
 #endif
     pdl_trigger();       // the next call's attention kernel may queue up behind this grid
-    pdl_wait();          // partials are complete and visible once the attention grid has finished
     const int units = a.row_blocks * a.Hkv;
     const int RPB = a.rows_per_block, Ev = a.Ev;
     // how many CTAs left a partial for this unit: from the header the attention kernel wrote
@@ -161,6 +166,9 @@ __global__ void __launch_bounds__(MW * 32) merge_kernel(const __grid_constant__ 
     const int nbases = a.world > 0 ? a.world : 1;
     const int hq_all = a.world > 0 ? a.world * a.Hq : a.Hq;       // heads of the destination tensor
     const int hq_off = a.world > 0 ? a.rank * a.Hq : 0;           // where this rank's heads start in it
+    pdl_wait();          // partials are complete and visible once the attention grid has finished
+    // (Running the whole merge once on stale data before the wait, nothing stored, so that its instructions are on the
+    // SM when the wait ends: measured +0.1 ... +0.5 us per call, not kept.)
 #pragma unroll 1
     for (int row = blockIdx.y * MW + warp; row < RPB; row += gridDim.y * MW) {
         const int gr = rb * RPB + row;
@@ -170,7 +178,7 @@ __global__ void __launch_bounds__(MW * 32) merge_kernel(const __grid_constant__ 
 #pragma unroll 1
         for (int e0 = 0; e0 < Ev; e0 += 128)
             merge_partials_rows<T, NSTAT, KB>(a.ws_o, a.ws_m, a.ws_l, (size_t)u * a.parts_per_unit, RPB, Ev, row, a.parts_per_unit,
-                                          count_of, bases, nbases, offset, lane, e0);
+                                              count_of, bases, nbases, offset, lane, e0);
     }
     HOGATT_SPAN_MAX(3);
 #ifdef HOGATT_TIMELINE
@@ -192,6 +200,9 @@ __global__ void __launch_bounds__(WW * 32) merge_wide_kernel(const __grid_consta
     const int rb = u / a.Hkv, hkv = u % a.Hkv;
     pdl_trigger();
     pdl_wait();
+#ifdef HOGATT_TIMELINE
+    if (threadIdx.x == 0) atomicMin(&g_mtrace[a.debug_id % kTraceCalls][0], global_timer_ns_());   // (here: the wait is over)
+#endif
     const int units = a.row_blocks * a.Hkv;
     const int RPB = a.rows_per_block, Ev = a.Ev;
     const int gr = rb * RPB + row;
@@ -297,16 +308,13 @@ __global__ void __launch_bounds__(WW * 32) merge_wide_kernel(const __grid_consta
         const int nbases = a.world > 0 ? a.world : 1;
         const int hq_all = a.world > 0 ? a.world * a.Hq : a.Hq, hq_off = a.world > 0 ? a.rank * a.Hq : 0;
         const size_t offset = ((size_t)(id.w * hq_all + hq_off + hkv * a.G + id.g) * a.S + id.s) * Ev + warp * 128 + lane * 4;
-        const T r0 = Scalar<T>::from_float(sum.x * inv), r1 = Scalar<T>::from_float(sum.y * inv);
-        const T r2 = Scalar<T>::from_float(sum.z * inv), r3 = Scalar<T>::from_float(sum.w * inv);
-        for (int b = 0; b < nbases; ++b) {
-            T* dst = (a.world > 0 ? static_cast<T*>(a.peer_out[b]) : local_out) + offset;
-            dst[0] = r0;
-            dst[1] = r1;
-            dst[2] = r2;
-            dst[3] = r3;
-        }
+        for (int b = 0; b < nbases; ++b)
+            store4<T>((a.world > 0 ? static_cast<T*>(a.peer_out[b]) : local_out) + offset, sum.x * inv, sum.y * inv, sum.z * inv,
+                      sum.w * inv);
     }
+#ifdef HOGATT_TIMELINE
+    if (threadIdx.x == 0) atomicMax(&g_mtrace[a.debug_id % kTraceCalls][1], global_timer_ns_());
+#endif
 }
 
 // Completion exchange of the fused output all-gather: one warp, lane p talks to rank p.
@@ -323,17 +331,28 @@ struct PeerFlags {
     int* f[HOGATT_MAX_PEERS];
 };
 __global__ void __launch_bounds__(32) gather_signal_kernel(const __grid_constant__ PeerFlags flags, int world, int rank,
-                                                           int* status) {
+                                                           int* status, int debug_id) {
     const int lane = threadIdx.x;
     int* mine = flags.f[rank];
     int epoch = 0;
+#ifdef HOGATT_TIMELINE
+    if (lane == 0) g_strace[debug_id % kTraceCalls][0] = global_timer_ns_();
+#endif
     pdl_trigger();       // the next call's attention kernel may be scheduled (it waits for this grid before it reads or writes anything of this call's)
     pdl_wait();          // the rows are out: the storing kernel has completed and its stores are flushed
+#ifdef HOGATT_TIMELINE
+    if (lane == 0) g_strace[debug_id % kTraceCalls][1] = global_timer_ns_();
+#endif
     if (lane == 0) epoch = atomicAdd(mine + world, 1) + 1;
     epoch = __shfl_sync(0xffffffffu, epoch, 0);
     if (lane < world) {
-        __threadfence_system();
+        // (the release store orders everything that happened before it -- the storing kernel's rows, complete and
+        // flushed at the kernel boundary -- in front of the count; with an explicit system fence in front of it as
+        // well, publishing took 3.3 us of a 20 us call on two GPUs, without it 1.8-2.3 us)
         asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flags.f[lane] + rank), "r"(epoch) : "memory");
+#ifdef HOGATT_TIMELINE
+        if (lane == 0) g_strace[debug_id % kTraceCalls][2] = global_timer_ns_();
+#endif
         const uint64_t t0 = global_timer_ns();
         while (true) {
             int seen;
@@ -346,6 +365,10 @@ __global__ void __launch_bounds__(32) gather_signal_kernel(const __grid_constant
             __nanosleep(100);
         }
     }
+#ifdef HOGATT_TIMELINE
+    __syncwarp();
+    if (lane == 0) g_strace[debug_id % kTraceCalls][3] = global_timer_ns_();
+#endif
 }
 
 // rq[f,w,h,s,:] = rope(q[w,h,s,:], cos[f,w,s,:], sin[f,w,s,:]).
