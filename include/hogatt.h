@@ -232,7 +232,8 @@ int hogatt_fused_launch_static(const hogatt_problem* p, hogatt_stream_t stream);
  * HOGATT_WAIT_LIMIT_MS in the environment shortens it), until all peers have published theirs.  When the
  * call's work has completed on a rank's stream, that rank's out_full is complete.
  *   out_full[p], flags[p]: rank p's buffers as mapped into THIS GPU's address space (CUDA IPC / VMM /
- *       symmetric memory); flags[p] is int32[world + 1], zero-filled once before the first call
+ *       symmetric memory); out_full[p] is 16-byte aligned (HOGATT_ERR_MISALIGNED otherwise);
+ *       flags[p] is int32[world + 1], zero-filled once before the first call
  *       (slots 0 .. world-1: the counts the ranks publish; slot world: rank p's own call counter).
  *   The caller must not let a rank start call k+1 on an out_full that another rank is still reading
  *   from call k (alternate two buffers, or synchronise the consumers).

@@ -638,8 +638,10 @@ int attention_launch(const hogatt_problem* p, bool fused, cudaStream_t stream, c
     if (peers) {
         if (peers->world < 1 || peers->world > HOGATT_MAX_PEERS || peers->rank < 0 || peers->rank >= peers->world)
             return HOGATT_ERR_BAD_SHAPE;
-        for (int i = 0; i < peers->world; ++i)
+        for (int i = 0; i < peers->world; ++i) {
             if (!peers->out_full[i] || !peers->flags[i]) return HOGATT_ERR_NULL_POINTER;
+            if (!aligned16(peers->out_full[i]) || ((uintptr_t)peers->flags[i] & 3u)) return HOGATT_ERR_MISALIGNED;
+        }
     }
     if (fused) {
         if (!p->cosines || !p->sines) return HOGATT_ERR_NULL_POINTER;

@@ -227,10 +227,11 @@ __global__ void __launch_bounds__(WW * 32) merge_wide_kernel(const __grid_consta
         float4 x[kPer];
         const bool wide = Ev > 128;
 #pragma unroll
-        for (int k = 0; k < kPer; ++k) {
-            const int p = min(p0 + k * WW, count - 1);
-            x[k] = lane * 4 < Ev ? __ldcg(reinterpret_cast<const float4*>(a.ws_o + ((slot0 + p) * RPB + row) * Ev + lane * 4))
-                                 : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int k = 0; k < kPer; ++k) {             // (only the partials that exist: with 39 per row a warp has ten, not 24)
+            const int p = p0 + k * WW;
+            x[k] = (lane * 4 < Ev && p < count)
+                       ? __ldcg(reinterpret_cast<const float4*>(a.ws_o + ((slot0 + p) * RPB + row) * Ev + lane * 4))
+                       : make_float4(0.f, 0.f, 0.f, 0.f);
         }
         float Mp = mp;
 #pragma unroll
