@@ -206,14 +206,21 @@ def time_steps(step_fn, steps: int, warmup: int, barrier):
     torch.cuda.synchronize()
     barrier()
     torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(steps):
+    # one event per step boundary: the total is what the line reports, the per-step spread goes beside it
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(steps + 1)]
+    ev[0].record()
+    for i in range(steps):
         step_fn()
-    e1.record()
+        ev[i + 1].record()
     torch.cuda.synchronize()
     barrier()
-    return e0.elapsed_time(e1) / 1e3      # seconds
+    per = sorted(ev[i].elapsed_time(ev[i + 1]) for i in range(steps))
+    pick = lambda q: per[min(len(per) - 1, int(q * len(per)))]
+    STEP_SPREAD.update(median_ms=round(pick(0.5), 5), p10_ms=round(pick(0.1), 5), p90_ms=round(pick(0.9), 5))
+    return ev[0].elapsed_time(ev[steps]) / 1e3      # seconds
+
+
+STEP_SPREAD = {}       # per-step times of the most recent time_steps() on this rank
 
 
 def run_ours(args):
@@ -320,6 +327,7 @@ def run_ours(args):
             if rank == 0 and primary:
                 sampler.start()
             secs = time_steps(step, steps, warmup, barrier)
+            spread = dict(STEP_SPREAD)
             clocks = sampler.stop() if (rank == 0 and primary) else None
 
             # attention-only time at N > 1 (no gather), for the split the scaling discussion needs
@@ -354,7 +362,7 @@ def run_ours(args):
         res = dict(secs=float(t[0]), secs_attn=float(t[1]) or None, n_calls=steps * len(calls), bytes_per_call=bytes_per_call,
                    launches_per_step=launches_per_step, graph=graph is not None, fused_gather=fused_gather, iso_us=iso_us,
                    clocks=clocks, full=full, layers=len(calls), kv_resident=int(sum(p.algorithmic_bytes() for p in probs)),
-                   parity=parity)
+                   parity=parity, spread=spread)
         del calls, probs, graph, gathered, peer_out, peer_tables
         torch.cuda.empty_cache()
         return res
@@ -381,6 +389,7 @@ def run_ours(args):
             e = {"us_per_call": round(t_call * 1e6, 3),
                  "value_TBps": round(x["bytes_per_call"] / t_call / 1e12, 4),
                  "attention_only_us_per_call": round(x["secs_attn"] / x["n_calls"] * 1e6, 3) if x["secs_attn"] else None,
+                 "us_per_call_spread": {k.replace("_ms", ""): round(v * 1e3 / x["layers"], 3) for k, v in x["spread"].items()},
                  "layers_per_step": x["layers"], "steps": steps, "bytes_per_call": x["bytes_per_call"],
                  "parity": x["parity"]}
             if name == "cfg5":
@@ -429,6 +438,7 @@ def run_ours(args):
         "config": job_config(args, wl.baseline_problem(args.workload).meta if world > 1 else full.meta, world,
                              fused_gather or world == 1, graph_used),
         "us_per_call": round(us_per_call, 3),
+        "us_per_call_spread": {k.replace("_ms", ""): round(v * 1e3 / (n_calls / args.steps), 3) for k, v in m["spread"].items()},
         "us_per_call_isolated_cold": round(iso_us, 3),
         "pct_of_nominal_8TBps": round(100 * value * 1e3 / (NOMINAL_HBM_GBS * world), 2),
         "gpu_launches": launches_per_step * args.steps,
