@@ -1058,6 +1058,10 @@ int hogatt_debug_trace(unsigned long long* out, unsigned long long* mout, int re
     }
     return HOGATT_OK;
 }
+int hogatt_debug_mphase(unsigned long long* out) {
+    HOGATT_CUDA_OK(cudaMemcpyFromSymbol(out, g_mphase, sizeof(g_mphase)));
+    return HOGATT_OK;
+}
 int hogatt_debug_strace(unsigned long long* out) {
     HOGATT_CUDA_OK(cudaMemcpyFromSymbol(out, g_strace, sizeof(g_strace)));
     return HOGATT_OK;

@@ -80,7 +80,8 @@ __device__ unsigned long long g_span[8];      // [0] attn first start, [1] attn 
 constexpr int kTraceCalls = 64, kTraceEvents = 8;
 __device__ unsigned long long g_trace[kTraceCalls][kTraceEvents][256];
 __device__ unsigned long long g_mtrace[kTraceCalls][2];
-__device__ unsigned long long g_strace[kTraceCalls][4];     // exchange kernel: start, predecessor done, published, peers seen
+__device__ unsigned long long g_strace[kTraceCalls][4];
+__device__ unsigned long long g_mphase[kTraceCalls][4][128];  // merge CTAs: start, wait over, first row combined, end     // exchange kernel: start, predecessor done, published, peers seen
 #define HOGATT_TRACE(id, ev) do { if (blockIdx.x < 256) g_trace[(id) % kTraceCalls][ev][blockIdx.x] = global_timer_ns_(); } while (0)
 #define HOGATT_SPAN_MIN(i) do { if (threadIdx.x == 0) atomicMin(&g_span[i], global_timer_ns_()); } while (0)
 #define HOGATT_SPAN_MAX(i) do { if (threadIdx.x == 0) atomicMax(&g_span[i], global_timer_ns_()); } while (0)

@@ -37,7 +37,7 @@ template <class T, int kMaxStat, int kBatch, class CountFn>
 __device__ __forceinline__ void merge_partials_rows(const float* __restrict__ ws_o, const float* __restrict__ ws_m,
                                                    const float* __restrict__ ws_l, size_t slot0, int rpb, int Ev,
                                                    int row, int slots, CountFn count_of, T* const* bases, int nbases,
-                                                   size_t offset, int lane, int e0) {
+                                                   size_t offset, int lane, int e0, unsigned long long* stamp = nullptr) {
     // kBatch: output partials fetched in the first round trip (24; 4 or 8 where a row never has more: a unit of
     // many query rows is cut into few partials, and a lean kernel keeps 16 CTAs per SM resident instead of 3).
     // kMaxStat: statistics held per lane (32 * kMaxStat partials per row without extra loads)
@@ -92,6 +92,9 @@ __device__ __forceinline__ void merge_partials_rows(const float* __restrict__ ws
             for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
             blind = !(den > 0.f);
             inv = blind ? 0.f : 1.f / den;
+#ifdef HOGATT_TIMELINE
+            if (stamp && lane == 0) *stamp = global_timer_ns_();      // the statistics have arrived
+#endif
         }
         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
@@ -148,6 +151,10 @@ __global__ void __launch_bounds__(MW * 32) merge_kernel(const __grid_constant__ 
 #ifdef HOGATT_TIMELINE
     if (threadIdx.x == 0) atomicMin(&g_mtrace[a.debug_id % kTraceCalls][0], global_timer_ns_());
 #endif
+#ifdef HOGATT_TIMELINE
+    const int mcta = blockIdx.y * gridDim.x + blockIdx.x;
+    if (threadIdx.x == 0 && mcta < 128) g_mphase[a.debug_id % kTraceCalls][0][mcta] = global_timer_ns_();
+#endif
     pdl_trigger();       // the next call's attention kernel may queue up behind this grid
     const int units = a.row_blocks * a.Hkv;
     const int RPB = a.rows_per_block, Ev = a.Ev;
@@ -167,6 +174,9 @@ __global__ void __launch_bounds__(MW * 32) merge_kernel(const __grid_constant__ 
     const int hq_all = a.world > 0 ? a.world * a.Hq : a.Hq;       // heads of the destination tensor
     const int hq_off = a.world > 0 ? a.rank * a.Hq : 0;           // where this rank's heads start in it
     pdl_wait();          // partials are complete and visible once the attention grid has finished
+#ifdef HOGATT_TIMELINE
+    if (threadIdx.x == 0 && mcta < 128) g_mphase[a.debug_id % kTraceCalls][1][mcta] = global_timer_ns_();
+#endif
     // (Running the whole merge once on stale data before the wait, nothing stored, so that its instructions are on the
     // SM when the wait ends: measured +0.1 ... +0.5 us per call, not kept.)
 #pragma unroll 1
@@ -177,11 +187,18 @@ __global__ void __launch_bounds__(MW * 32) merge_kernel(const __grid_constant__ 
         const size_t offset = ((size_t)(id.w * hq_all + hq_off + hkv * a.G + id.g) * a.S + id.s) * Ev;
 #pragma unroll 1
         for (int e0 = 0; e0 < Ev; e0 += 128)
+#ifdef HOGATT_TIMELINE
+            merge_partials_rows<T, NSTAT, KB>(a.ws_o, a.ws_m, a.ws_l, (size_t)u * a.parts_per_unit, RPB, Ev, row, a.parts_per_unit,
+                                              count_of, bases, nbases, offset, lane, e0,
+                                              (warp == 0 && mcta < 128) ? &g_mphase[a.debug_id % kTraceCalls][2][mcta] : nullptr);
+#else
             merge_partials_rows<T, NSTAT, KB>(a.ws_o, a.ws_m, a.ws_l, (size_t)u * a.parts_per_unit, RPB, Ev, row, a.parts_per_unit,
                                               count_of, bases, nbases, offset, lane, e0);
+#endif
     }
     HOGATT_SPAN_MAX(3);
 #ifdef HOGATT_TIMELINE
+    if (threadIdx.x == 0 && mcta < 128) g_mphase[a.debug_id % kTraceCalls][3][mcta] = global_timer_ns_();
     if (threadIdx.x == 0) atomicMax(&g_mtrace[a.debug_id % kTraceCalls][1], global_timer_ns_());
 #endif
 }
