@@ -115,3 +115,34 @@ def test_cache_step_structs_match_the_header_and_refuse_bad_arguments(lib):
     assert lib.hogatt_step_plan_launch(C.byref(sp), None) == -1          # no pointers at all
     ap = _cabi.Append()
     assert lib.hogatt_append_launch(C.byref(ap), None) == -1
+
+
+def test_ctypes_mirrors_agree_with_the_compiler(tmp_path):
+    """Every struct of include/hogatt.h, field by field, as a C compiler lays it out against its ctypes mirror: a
+    plain C program that includes the header prints ``sizeof`` and every ``offsetof``."""
+    import shutil
+    import subprocess
+    cc = shutil.which("gcc") or shutil.which("cc")
+    if cc is None:
+        pytest.skip("no C compiler")
+    pairs = [("hogatt_problem", _cabi.Problem), ("hogatt_paged_problem", _cabi.PagedProblem), ("hogatt_peers", _cabi.Peers),
+             ("hogatt_step_plan", _cabi.StepPlan), ("hogatt_append", _cabi.Append)]
+    lines = ['#include <stdio.h>', '#include <stddef.h>', '#include "hogatt.h"', "int main(void) {"]
+    for cname, mirror in pairs:
+        lines.append(f'  printf("{cname} sizeof %zu\\n", sizeof({cname}));')
+        for field, _ in mirror._fields_:
+            lines.append(f'  printf("{cname} {field} %zu\\n", offsetof({cname}, {field}));')
+    lines += ["  return 0;", "}"]
+    src = tmp_path / "layout.c"
+    src.write_text("\n".join(lines))
+    exe = tmp_path / "layout"
+    subprocess.run([cc, "-std=c99", "-Wall", "-Werror", "-I", os.path.join(ROOT, "include"), str(src), "-o", str(exe)], check=True)
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout
+    seen = {}
+    for ln in out.splitlines():
+        cname, field, value = ln.split()
+        seen[(cname, field)] = int(value)
+    for cname, mirror in pairs:
+        assert seen[(cname, "sizeof")] == C.sizeof(mirror), cname
+        for field, _ in mirror._fields_:
+            assert seen[(cname, field)] == getattr(mirror, field).offset, (cname, field)
