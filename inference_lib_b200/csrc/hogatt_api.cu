@@ -244,6 +244,38 @@ int64_t tiles_upper_bound(const hogatt_problem* p, const Resolved& r) {
     return th;
 }
 
+// How many query rows a CTA of the mma.sync kernel keeps (16, 32 or 64): resolve() takes the smallest block that
+// holds all W*G*S rows of a kv head, so that every key is fetched once.  With few kv heads and a short context that
+// leaves each CTA one or two tiles behind a start-up that grows with the block (query rows to rotate and stage,
+// warps to fold, partials per row to merge), and smaller blocks -- more units, every key fetched once per row block,
+// the repeats served by L2 since the row blocks of a head walk the keys together -- are faster.  Fitted on B200
+// (microseconds per call, n = tiles per CTA): 16 rows 9.0 + 1.03 n, 32 rows 13.4 + 1.27 n, 64 rows 18.5 + 2.64 n;
+// e.g. 64 rows over 2 kv heads and 16 K keys: 23.1 us as one 64-row block (n = 1.7), 17.8 as two of 32, 16.1 as
+// four of 16 (n = 6.9); 20 rows over 8 kv heads stay one 32-row block (22.2 against 23.2 us).
+void refine_row_blocks(const hogatt_problem* p, Resolved* r, int grid, int64_t tiles_per_unit) {
+    if (r->kernel != HOGATT_KERNEL_MMA || r->cluster_forced || r->mt <= 1 || tiles_per_unit <= 0 || grid <= 0) return;
+    static const float kFixed[3] = {9.0f, 13.4f, 18.5f}, kPerTile[3] = {1.03f, 1.27f, 2.64f};
+    const int64_t rows_total = (int64_t)p->W * (p->Hq / p->Hkv) * p->S;
+    // (fitted on calls of a few tiles per CTA and only applied there: with many tiles per CTA the largest block,
+    // which fetches every key once, stays)
+    if ((int64_t)r->units * tiles_per_unit >= (int64_t)8 * grid) return;
+    int best = r->mt;
+    float best_t = 0.f;
+    for (int i = 0, mt = 1; mt <= r->mt; ++i, mt *= 2) {
+        const int64_t blocks = (rows_total + 16 * mt - 1) / (16 * mt);
+        const float t = kFixed[i] + kPerTile[i] * (float)(blocks * p->Hkv * tiles_per_unit) / (float)grid;
+        if (mt == 1 || t < best_t) {
+            best = mt;
+            best_t = t;
+        }
+    }
+    if (best == r->mt) return;
+    r->mt = best;
+    r->rows_per_block = 16 * best;
+    r->row_blocks = (int)((rows_total + r->rows_per_block - 1) / r->rows_per_block);
+    r->units = r->row_blocks * p->Hkv;
+}
+
 int grid_size(const hogatt_problem* p, int sms) {
     int grid = sms;
     if (p->max_ctas > 0 && p->max_ctas < grid) grid = p->max_ctas;
@@ -660,6 +692,7 @@ int attention_launch(const hogatt_problem* p, bool fused, cudaStream_t stream, c
     rc = current_device_info(&dev, &sms, &smem_optin);
     if (rc != HOGATT_OK) return rc;
     const int grid = grid_size(p, sms);
+    refine_row_blocks(p, &r, grid, tiles_upper_bound(p, r));
     const WorkspaceLayout w = carve(p, r, grid);
     if (p->workspace_bytes < w.total) return HOGATT_ERR_WORKSPACE_TOO_SMALL;
     r.cluster = choose_cluster(p, r, dev, sms, smem_optin, tiles_upper_bound(p, r));
@@ -898,7 +931,21 @@ size_t hogatt_workspace_bytes(const hogatt_problem* p) {
     if (resolve(p, &r) != HOGATT_OK) return 0;
     int dev, sms, smem_optin;
     if (current_device_info(&dev, &sms, &smem_optin) != HOGATT_OK) return 0;
-    return carve(p, r, grid_size(p, sms)).total;
+    const int grid = grid_size(p, sms);
+    size_t need = carve(p, r, grid).total;
+    if (r.kernel == HOGATT_KERNEL_MMA && !r.cluster_forced) {
+        // a launch may cut the query rows into smaller blocks than resolve() did (refine_row_blocks): room for any of them
+        const int64_t rows_total = (int64_t)p->W * (p->Hq / p->Hkv) * p->S;
+        for (int mt = 1; mt < r.mt; mt *= 2) {
+            Resolved q = r;
+            q.mt = mt;
+            q.rows_per_block = 16 * mt;
+            q.row_blocks = (int)((rows_total + q.rows_per_block - 1) / q.rows_per_block);
+            q.units = q.row_blocks * p->Hkv;
+            need = std::max(need, carve(p, q, grid).total);
+        }
+    }
+    return need;
 }
 
 int hogatt_sdpa_launch(const hogatt_problem* p, hogatt_stream_t stream) {
@@ -1086,6 +1133,7 @@ int hogatt_plan_describe(const hogatt_problem* p, const int32_t* visible_rows, i
     for (int f = 0; f < p->F; ++f) th += ceil_div(visible_rows[f] < 0 ? 0 : visible_rows[f], r.tile_tokens);
     if (th > (1 << 30)) return HOGATT_ERR_TOO_LARGE;
     const int grid = grid_size(p, num_sms);
+    refine_row_blocks(p, &r, grid, th);
     const int cluster = r.cluster_forced ? cluster_upper_bound(r, num_sms) : 0;
     if (r.cluster_forced && cluster == 0) return HOGATT_ERR_BAD_KERNEL_CHOICE;
     plan[0] = r.tile_tokens;
@@ -1183,6 +1231,7 @@ int hogatt_launch_shape(const hogatt_problem* p, int32_t shape[4]) {
     rc = current_device_info(&dev, &sms, &smem_optin);
     if (rc != HOGATT_OK) return rc;
     const int grid = grid_size(p, sms);
+    refine_row_blocks(p, &r, grid, tiles_upper_bound(p, r));
     const int cluster = choose_cluster(p, r, dev, sms, smem_optin, tiles_upper_bound(p, r));
     if (r.cluster_forced && cluster == 0) return HOGATT_ERR_BAD_KERNEL_CHOICE;
     shape[0] = cluster ? HOGATT_KERNEL_MMA_CLUSTER : r.kernel;

@@ -163,7 +163,7 @@ __global__ void __launch_bounds__(kFmaThreads) paged_attention_kernel(const __gr
                 const int tok = i / kvr, c = i - tok * kvr;
                 if (tok < ntok) {
                     const int l = tok0 + tok;
-                    const size_t row = ((size_t)table[l / a.block_size] * a.Hkv + u.hkv) * a.block_size + l % a.block_size;
+                    const size_t row = ((size_t)table[min(l / a.block_size, a.max_blocks - 1)] * a.Hkv + u.hkv) * a.block_size + l % a.block_size;
                     const int4 raw = __ldg(reinterpret_cast<const int4*>(static_cast<const T*>(a.kcache) + row * E) + c);
                     const T* x = reinterpret_cast<const T*>(&raw);
 #pragma unroll
@@ -175,7 +175,7 @@ __global__ void __launch_bounds__(kFmaThreads) paged_attention_kernel(const __gr
                 int4 raw = make_int4(0, 0, 0, 0);                     // rows past the tile end must be finite
                 if (tok < ntok) {
                     const int l = tok0 + tok;
-                    const size_t row = ((size_t)table[l / a.block_size] * a.Hkv + u.hkv) * a.block_size + l % a.block_size;
+                    const size_t row = ((size_t)table[min(l / a.block_size, a.max_blocks - 1)] * a.Hkv + u.hkv) * a.block_size + l % a.block_size;
                     raw = __ldg(reinterpret_cast<const int4*>(static_cast<const T*>(a.vcache) + row * EV) + c);
                 }
                 const T* x = reinterpret_cast<const T*>(&raw);
@@ -289,7 +289,8 @@ __global__ void __launch_bounds__(PagedMmaCfg<HD, NS>::THREADS) paged_mma_kernel
             const int tok = warp * RW + (j % RW) + (j / RW) * RP;
             const int l = tok0 + (tok < ntok ? tok : 0);
             const int blk = l / a.block_size;
-            mine = ((long long)table[blk] * a.Hkv + u.hkv) * a.block_size + (l - blk * a.block_size);
+            // (a length beyond the block table is the caller's error; the lookup stays inside the table regardless)
+            mine = ((long long)table[min(blk, a.max_blocks - 1)] * a.Hkv + u.hkv) * a.block_size + (l - blk * a.block_size);
         }
         const int c = lane % CPR, sub = lane / CPR;
 #pragma unroll

@@ -146,3 +146,20 @@ def test_ctypes_mirrors_agree_with_the_compiler(tmp_path):
         assert seen[(cname, "sizeof")] == C.sizeof(mirror), cname
         for field, _ in mirror._fields_:
             assert seen[(cname, field)] == getattr(mirror, field).offset, (cname, field)
+
+
+def test_short_calls_with_few_kv_heads_get_smaller_row_blocks(lib):
+    """64 query rows per kv head, 2 kv heads: as one 64-row block a CTA would get 1.7 tiles behind the largest
+    start-up; the plan cuts the rows into four 16-row blocks (8 units, 6.9 tiles per CTA).  Long contexts and shapes
+    where the larger block wins keep it."""
+    dims = dict(F=5, W=4, Hq=32, Hkv=2, E=128, Ev=128, S=1, dtype=_cabi.BF16)
+    rc, plan = _describe(lib, [8192, 2048, 2048, 2048, 2048], **dims)
+    assert rc == 0 and plan[7] == _cabi.KERNEL_MMA and (plan[1], plan[2], plan[4]) == (16, 4, 8)
+    rc, plan = _describe(lib, [8 * 8192] + [8 * 2048] * 4, **dims)                  # 1,024 tiles per unit: every key once
+    assert rc == 0 and (plan[1], plan[2], plan[4]) == (64, 1, 2)
+    # 20 rows over 8 kv heads (GQA 5): one 32-row block stays faster than two of 16
+    rc, plan = _describe(lib, [8192, 2048, 2048, 2048, 2048], F=5, W=4, Hq=40, Hkv=8, E=128, Ev=128, S=1, dtype=_cabi.BF16)
+    assert rc == 0 and (plan[1], plan[2], plan[4]) == (32, 1, 8)
+    # ... but not when the kv heads are spread over 8 GPUs (one head here: under one tile per CTA)
+    rc, plan = _describe(lib, [8192, 2048, 2048, 2048, 2048], F=5, W=4, Hq=5, Hkv=1, E=128, Ev=128, S=1, dtype=_cabi.BF16)
+    assert rc == 0 and (plan[1], plan[2], plan[4]) == (16, 2, 2)
