@@ -74,7 +74,9 @@ typedef enum hogatt_status {
  * measured shape, its merge step folding any number of partials per row in one memory round trip);
  * MMA_CLUSTER forces the cluster shape (HOGATT_ERR_BAD_KERNEL_CHOICE when there are more units than half
  * the SMs, or the device cannot hold one cluster per unit at once).  hogatt_launch_shape() tells which one
- * a problem gets.
+ * a problem gets.  A CTA keeps 16, 32 or 64 query rows of a kv head: normally the smallest block that holds
+ * all W x Hq/Hkv x S of them (every key is then fetched once), smaller blocks for short calls with few kv
+ * heads, where they are faster (hogatt_plan_describe reports the outcome).
  *
  * DENSE is the kernel for calls with many query rows per kv head (W x Hq/Hkv x S >= 128, e.g. workers that
  * each issue a 16-token chunk), where the op is bound by the tensor pipe, not by HBM: 128-row query blocks,
@@ -170,7 +172,8 @@ int hogatt_last_cuda_error(void);
 /*
  * Scratch bytes hogatt_sdpa_launch / hogatt_fused_launch need for this problem on the current
  * device (split-K partial sums and their softmax statistics).  Only the dims, dtype, kernel and
- * max_ctas fields are read.  Returns 0 for an invalid problem.
+ * max_ctas fields are read; the figure covers every launch shape a launch with these fields may
+ * pick.  Returns 0 for an invalid problem.
  * Stands in for the grow-only static workspace of src/kernels/kernel_v21.cuh:969-980.
  */
 size_t hogatt_workspace_bytes(const hogatt_problem* p);
