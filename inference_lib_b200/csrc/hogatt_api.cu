@@ -751,6 +751,12 @@ int attention_launch(const hogatt_problem* p, bool fused, cudaStream_t stream, c
         args.host_plan = 1;
         args.plan_tiles = (int)plan_tiles;
         args.plan_ctas = effective_ctas(plan_tiles * r.units, grid);
+        if (r.kernel == HOGATT_KERNEL_MMA) {         // ranges that stay inside one fragment of one unit, where the lengths allow
+            int pre[HOGATT_MAX_FRAGMENTS + 1];
+            pre[0] = 0;
+            for (int f = 0; f < p->F; ++f) pre[f + 1] = pre[f] + ceil_div(args.ft.e[f].vis, r.tile_tokens);
+            args.plan_ctas = aligned_ctas(pre, p->F, r.units, grid);
+        }
         args.stable_fragments = pdl_enabled() ? std::max(0, std::min(p->F, p->stable_fragments)) : 0;
     }
 
@@ -1142,6 +1148,12 @@ int hogatt_plan_describe(const hogatt_problem* p, const int32_t* visible_rows, i
     plan[3] = (int)th;
     plan[4] = r.units;
     plan[5] = cluster ? r.units * cluster : effective_ctas((int64_t)r.units * th, grid);
+    if (!cluster && r.kernel == HOGATT_KERNEL_MMA) {
+        int pre[HOGATT_MAX_FRAGMENTS + 1];
+        pre[0] = 0;
+        for (int f = 0; f < p->F; ++f) pre[f + 1] = pre[f] + ceil_div(visible_rows[f] < 0 ? 0 : visible_rows[f], r.tile_tokens);
+        plan[5] = aligned_ctas(pre, p->F, r.units, grid);
+    }
     plan[6] = cluster ? cluster : max_parts_per_unit(r.units, grid);
     plan[7] = cluster ? HOGATT_KERNEL_MMA_CLUSTER : r.kernel;
     return HOGATT_OK;

@@ -285,7 +285,7 @@ dense_attention_kernel(const __grid_constant__ KernelArgs a, const __grid_consta
     const int TH = pre[a.F];
     const int units = a.row_blocks * a.Hkv;
     const int64_t N = (int64_t)units * TH;
-    const int ctas = effective_ctas(N, gridDim.x);
+    const int ctas = a.host_plan ? a.plan_ctas : effective_ctas(N, gridDim.x);
     if (!a.host_plan && blockIdx.x == 0 && tid == 0) {
         a.header[0] = TH;
         a.header[1] = ctas;

@@ -209,7 +209,7 @@ mma_attention_kernel(const __grid_constant__ KernelArgs a, const int use_evict_f
     const int TH = pre[a.F];
     const int units = a.row_blocks * a.Hkv;
     const int64_t N = (int64_t)units * TH;
-    const int ctas = CL ? (int)gridDim.x : effective_ctas(N, gridDim.x);
+    const int ctas = CL ? (int)gridDim.x : (a.host_plan ? a.plan_ctas : aligned_ctas(pre, a.F, units, gridDim.x));
     const int CS = CL ? (int)cluster_nctarank() : 1, crank = CL ? (int)cluster_ctarank() : 0;
     if (!CL && !a.host_plan && blockIdx.x == 0 && tid == 0) {      // (host plan: the merge kernel has both as arguments)
         a.header[0] = TH;

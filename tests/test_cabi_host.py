@@ -52,7 +52,12 @@ def test_plan_for_the_headline_shapes(lib):
     rc, plan = _describe(lib, [8192, 2048, 2048, 2048, 2048], F=5, W=4, Hq=32, Hkv=8, E=128, Ev=128, S=1, dtype=_cabi.BF16)
     assert rc == 0
     tile, rows, row_blocks, th, units, ctas, parts, kernel = plan
-    assert (tile, rows, row_blocks, th, units, ctas, parts, kernel) == (128, 16, 1, 128, 8, 148, 148 // 8 + 2, _cabi.KERNEL_MMA)
+    # 1,024 tiles: 128 CTAs of exactly 8 tiles (8 divides the 64 + 4 x 16 tiles of a unit), so that no CTA's range
+    # crosses a fragment or kv-head boundary; the workspace keeps room for 148 // 8 + 2 partials per unit
+    assert (tile, rows, row_blocks, th, units, ctas, parts, kernel) == (128, 16, 1, 128, 8, 128, 148 // 8 + 2, _cabi.KERNEL_MMA)
+    # ragged lengths: no common tile count, balanced ranges over all SMs
+    rc, plan = _describe(lib, [8192, 2000, 2100, 1500, 2048], F=5, W=4, Hq=32, Hkv=8, E=128, Ev=128, S=1, dtype=_cabi.BF16)
+    assert rc == 0 and plan[5] == 148
     # the cluster launch shape only on request: one cluster of up to 16 CTAs per kv head, merged inside the kernel
     rc, plan = _describe(lib, [8192, 2048, 2048, 2048, 2048], F=5, W=4, Hq=32, Hkv=8, E=128, Ev=128, S=1, dtype=_cabi.BF16,
                          kernel=_cabi.KERNEL_MMA_CLUSTER)
