@@ -40,7 +40,7 @@ NOMINAL_HBM_GBS = 8000.0
 # dram__bytes_read.sum + dram__bytes_write.sum of the attention kernel divided by its algorithmic bytes, per workload,
 # from the ncu captures summarised under profiles/ (mma_attention_kernel_target.md, ..._cfg2_cfg3_cfg4.md).  Only a
 # single-GPU run of a captured shape at its full length reports `traffic`; everything else reports null.
-NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = {"target": 1.0146, "cfg2": 1.0017, "cfg3": 1.0191, "cfg4": 1.0082}
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = {"target": 1.0072, "cfg2": 1.0017, "cfg3": 1.0191, "cfg4": 1.0082}
 FALLBACK_HBM_GBS = 6650.0
 
 
