@@ -67,8 +67,9 @@ typedef enum hogatt_status {
 
 /* Which device code runs.  AUTO picks the tensor-core kernel for f16/bf16 with E == Ev in {64, 128}
  * and the FMA kernel for everything else (fp32, other head sizes).  The tensor-core kernel has two
- * launch shapes: a persistent grid (one CTA per SM over balanced tile ranges, partial results in the
- * workspace, a merge kernel after it) and a thread-block-cluster grid (one cluster per kv head and row
+ * launch shapes: a persistent grid (one CTA per SM over balanced tile ranges -- or fewer CTAs of one
+ * common whole number of tiles each, where that keeps every range inside one fragment -- partial results
+ * in the workspace, a merge kernel after it) and a thread-block-cluster grid (one cluster per kv head and row
  * block, partial results merged through distributed shared memory inside the same kernel, nothing
  * written to the workspace).  AUTO and MMA take the persistent grid (on B200 it is the faster one at every
  * measured shape, its merge step folding any number of partials per row in one memory round trip);
