@@ -20,7 +20,9 @@
 //     rings (measured 166 -> 157 us per 1,024-row group) -- and keep the running max and sum in registers.  (Measured
 //     and not kept: the query tile as a tensor-memory operand too, 176 us; two query buffers with a segment-ahead fetch
 //     at the price of a two-stage K ring, +4 us; two softmax groups taking the tiles in turn, one thread per row,
-//     +20 us; programmatic dependent launch behind the rotation kernel, +3 us.)  O is rescaled in tensor memory only when a row's
+//     +20 us; programmatic dependent launch behind the rotation kernel, +3 us; half of a tile's exponentials as a cubic on
+//     the FMA pipe instead of the special-function unit, +7 us: the softmax threads are bound by issue slots and
+//     latency, not by ex2 throughput.)  O is rescaled in tensor memory only when a row's
 //     max has grown by more than 2^8 since the scale it is stored at (then exp2 arguments stay below 8 and
 //     nothing overflows); the stored scale travels with the partial result, so the merge is exact.
 //
