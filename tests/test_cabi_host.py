@@ -168,3 +168,26 @@ def test_short_calls_with_few_kv_heads_get_smaller_row_blocks(lib):
     # ... but not when the kv heads are spread over 8 GPUs (one head here: under one tile per CTA)
     rc, plan = _describe(lib, [8192, 2048, 2048, 2048, 2048], F=5, W=4, Hq=5, Hkv=1, E=128, Ev=128, S=1, dtype=_cabi.BF16)
     assert rc == 0 and (plan[1], plan[2], plan[4]) == (16, 2, 2)
+
+
+@pytest.mark.parametrize("lengths,dims", [
+    ([8192, 2048, 2048, 2048, 2048], dict(F=5, W=4, Hq=32, Hkv=8, E=128, Ev=128, S=1)),        # the north-star shape
+    ([4096, 2048, 2048], dict(F=3, W=2, Hq=32, Hkv=8, E=128, Ev=128, S=1)),                    # cfg2
+    ([8192, 2048, 2048, 2048, 2048], dict(F=5, W=4, Hq=16, Hkv=4, E=128, Ev=128, S=1)),        # one of two ranks' share
+])
+def test_aligned_ranges_stay_inside_one_fragment_of_one_unit(lib, lengths, dims):
+    rc, plan = _describe(lib, lengths, dtype=_cabi.BF16, **dims)
+    assert rc == 0
+    tile, th, units, ctas = plan[0], plan[3], plan[4], plan[5]
+    assert ctas < 148 and (th * units) % ctas == 0, "a whole number of tiles per CTA"
+    bounds, acc = [], 0
+    for n in lengths:
+        acc += -(-n // tile)
+        bounds.append(acc)
+    rng = (C.c_int64 * 4)()
+    for c in range(ctas):
+        assert lib.hogatt_plan_ranges(th, units, ctas, c, 0, rng) == 0
+        a, b = rng[0], rng[1] - 1                                   # first and last tile of the range
+        assert a // th == b // th, "a range must not run on into the next kv head"
+        seg = lambda t: next(i for i, e in enumerate(bounds) if t % th < e)
+        assert seg(a) == seg(b), "a range must not run on into the next fragment"
