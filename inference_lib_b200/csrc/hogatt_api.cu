@@ -455,13 +455,18 @@ int launch_fma_dims(const KernelArgs& args, int dev, int smem_optin, int grid, c
 // instead of one per 24 partials), as long as that grid stays small; otherwise the batched one-warp-per-row kernel.
 template <class T>
 int launch_merge(const KernelArgs& args, const Resolved& r, cudaStream_t stream) {
-    if (args.parts_per_unit > 32 && (int64_t)r.units * r.rows_per_block <= 4096) {
+    // Partials a row can have: what the workspace reserves per unit, or -- under a host plan, where the CTA count is
+    // known here -- what the ranges can actually leave (exactly ctas / units when that divides: aligned ranges).
+    int bound = args.parts_per_unit;
+    if (args.host_plan && r.units > 0)
+        bound = std::min(bound, ceil_div(args.plan_ctas, r.units) + (args.plan_ctas % r.units == 0 ? 0 : 1));
+    if (bound > 32 && (int64_t)r.units * r.rows_per_block <= 4096) {
         dim3 wgrid((unsigned)r.units, (unsigned)r.rows_per_block);
         // Four warps (128 threads x 128 registers) fit on an SM beside a resident attention CTA, eight do not: with
-        // up to 24 partials per warp in one round trip, four serve up to 96 partials per row (kv heads over 2 or 4
-        // GPUs: 39, 76; measured 15.6 -> 14.4 us per call for one of two ranks' share at 16 K keys); a unit cut into
-        // 148 partials needs the eight (four take two round trips: 8.7 -> 9.3 us).
-        if (args.parts_per_unit <= 4 * 24)
+        // up to 24 partials per warp in one round trip, four serve up to 96 partials per row (kv heads over 4 GPUs:
+        // 64-76); a unit cut into 128-148 partials needs the eight (four take two round trips: 8.7 -> 9.3 us).  (Two
+        // round trips of 32 on the one-warp-per-row kernel instead, for 33-64 partials: 12.2 us against 9.6.)
+        if (bound <= 4 * 24)
             HOGATT_CUDA_OK(launch_kernel(merge_wide_kernel<T, 4>, wgrid, dim3(4 * 32), 0, stream, args));
         else
             HOGATT_CUDA_OK(launch_kernel(merge_wide_kernel<T>, wgrid, dim3(kWideWarps * 32), 0, stream, args));
@@ -472,13 +477,20 @@ int launch_merge(const KernelArgs& args, const Resolved& r, cudaStream_t stream)
         HOGATT_CUDA_OK(launch_kernel(merge_kernel<T, 1, 4>, mgrid, dim3(kMergeWarps * 32), 0, stream, args));
     else if (args.parts_per_unit <= 8)
         HOGATT_CUDA_OK(launch_kernel(merge_kernel<T, 1, 8>, mgrid, dim3(kMergeWarps * 32), 0, stream, args));
-    else if (args.parts_per_unit <= 32) {
-        // Two warps per CTA: 64 threads x 156 registers fit on an SM BESIDE a resident attention CTA (192 threads x 255
-        // registers leave 16 K registers), four warps do not.  With programmatic dependent launch that decides whether
-        // this grid is already resident when the attention grid drains, and whether the next call's attention CTAs can
-        // start on the SMs this grid occupies (measured: 18.8 -> 17.2 us per call at 16 K keys, 24.2 -> 22.2 at GQA 5).
+    else if (bound <= 32) {
+        // One warp per row, two warps per CTA: 64 threads x 150-190 registers fit on an SM BESIDE a resident attention
+        // CTA (192 threads x 255 registers leave 16 K registers), four warps do not.  With programmatic dependent
+        // launch that decides whether this grid is already resident when the attention grid drains, and whether the
+        // next call's attention CTAs can start on the SMs this grid occupies (measured: 18.8 -> 17.2 us per call at
+        // 16 K keys, 24.2 -> 22.2 at GQA 5).  The first round trip fetches 16, 24 or 32 partials per row; the fewer
+        // loads a warp issues the sooner they are back (16 instead of 24 at 16 partials per row: -0.3 us per call).
         dim3 g2((unsigned)r.units, (unsigned)ceil_div(r.rows_per_block, 2));
-        HOGATT_CUDA_OK(launch_kernel(merge_kernel<T, 1, 24, 2>, g2, dim3(64), 0, stream, args));
+        if (bound <= 16)
+            HOGATT_CUDA_OK(launch_kernel(merge_kernel<T, 1, 16, 2>, g2, dim3(64), 0, stream, args));
+        else if (bound <= 24)
+            HOGATT_CUDA_OK(launch_kernel(merge_kernel<T, 1, 24, 2>, g2, dim3(64), 0, stream, args));
+        else
+            HOGATT_CUDA_OK(launch_kernel(merge_kernel<T, 1, 32, 2>, g2, dim3(64), 0, stream, args));
     }
     else
         HOGATT_CUDA_OK(launch_kernel(merge_kernel<T, 5>, mgrid, dim3(kMergeWarps * 32), 0, stream, args));

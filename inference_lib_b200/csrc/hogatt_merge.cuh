@@ -108,7 +108,7 @@ __device__ __forceinline__ void merge_partials_rows(const float* __restrict__ ws
         }
         // more partials: one round trip per further batch.  The lean instantiation (at most 32 partials) only has
         // 8 left; it is kept small on purpose -- this kernel runs for 2.5 us and its instruction fetch shows.
-        constexpr int kNext = (kMaxStat == 1 && kBatch > 16) ? 32 - kBatch : kBatch;
+        constexpr int kNext = (kMaxStat == 1 && kBatch > 16) ? (kBatch < 32 ? 32 - kBatch : 8) : kBatch;   // (never 0: the loop must advance)
 #pragma unroll 1
         for (int p0 = kBatch; p0 < count; p0 += kNext) {
 #pragma unroll
