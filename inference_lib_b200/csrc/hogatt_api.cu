@@ -462,11 +462,14 @@ int launch_merge(const KernelArgs& args, const Resolved& r, cudaStream_t stream)
         bound = std::min(bound, ceil_div(args.plan_ctas, r.units) + (args.plan_ctas % r.units == 0 ? 0 : 1));
     if (bound > 32 && (int64_t)r.units * r.rows_per_block <= 4096) {
         dim3 wgrid((unsigned)r.units, (unsigned)r.rows_per_block);
-        // Four warps (128 threads x 128 registers) fit on an SM beside a resident attention CTA, eight do not: with
-        // up to 24 partials per warp in one round trip, four serve up to 96 partials per row (kv heads over 4 GPUs:
-        // 64-76); a unit cut into 128-148 partials needs the eight (four take two round trips: 8.7 -> 9.3 us).  (Two
-        // round trips of 32 on the one-warp-per-row kernel instead, for 33-64 partials: 12.2 us against 9.6.)
-        if (bound <= 4 * 24)
+        // One CTA per row.  Up to 64 partials: four warps x 16 partials under 102 registers, a CTA that fits on an SM
+        // beside a resident attention CTA (0.04-0.2 us per call over the next one); up to 96: four warps x 24 (168
+        // registers); 128-148 (one kv head per GPU): eight warps x 24 -- four warps would take two round trips there
+        // (8.7 -> 9.3 us per call).  (Two round trips of 32 on the one-warp-per-row kernel instead, for 33-64 partials:
+        // 12.2 us against 9.6.)
+        if (bound <= 4 * 16)
+            HOGATT_CUDA_OK(launch_kernel(merge_wide_kernel<T, 4, 16>, wgrid, dim3(4 * 32), 0, stream, args));
+        else if (bound <= 4 * 24)
             HOGATT_CUDA_OK(launch_kernel(merge_wide_kernel<T, 4>, wgrid, dim3(4 * 32), 0, stream, args));
         else
             HOGATT_CUDA_OK(launch_kernel(merge_wide_kernel<T>, wgrid, dim3(kWideWarps * 32), 0, stream, args));

@@ -208,8 +208,8 @@ __global__ void __launch_bounds__(MW * 32) merge_kernel(const __grid_constant__ 
 // maximum, denominator and weighted sum: one memory round trip for up to 192 partials per row), the eight results are
 // combined through shared memory.  The one-warp-per-row kernel above needs a round trip per 24 partials.
 constexpr int kWideWarps = 8;
-template <class T, int WW = kWideWarps>
-__global__ void __launch_bounds__(WW * 32) merge_wide_kernel(const __grid_constant__ KernelArgs a) {
+template <class T, int WW = kWideWarps, int KP = 24>
+__global__ void __launch_bounds__(WW * 32, (WW == 4 && KP == 16) ? 5 : 1) merge_wide_kernel(const __grid_constant__ KernelArgs a) {
     __shared__ float sm_m[WW], sm_l[WW];
     __shared__ float4 sm_o[WW][64];               // up to 256 output columns
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -231,7 +231,9 @@ __global__ void __launch_bounds__(WW * 32) merge_wide_kernel(const __grid_consta
         if (TH > 0) unit_ctas(u, TH, (int64_t)units * TH, ctas, &first, &count);
     }
     const size_t slot0 = (size_t)u * a.parts_per_unit;
-    constexpr int kPer = 24;                               // partials per warp per pass
+    // partials per warp per pass.  (Four warps x 16 under 102 registers make a CTA of 13 K registers, which fits on an
+    // SM beside a resident attention CTA; with 24 per warp the kernel takes 168 registers.)
+    constexpr int kPer = KP;
     float M = -INFINITY, L = 0.f;
     float4 acc[2] = {make_float4(0.f, 0.f, 0.f, 0.f), make_float4(0.f, 0.f, 0.f, 0.f)};     // columns lane*4 (+128)
 #pragma unroll 1
