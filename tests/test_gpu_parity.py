@@ -231,3 +231,20 @@ def test_bad_arguments_are_refused_without_launching():
     assert _cabi.launch(bp) == -1
     torch.cuda.synchronize()
     assert (out == 0).all(), "a refused call must not touch the output"
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("name", ["target", "cfg3"])
+@pytest.mark.parametrize("host_plan", [True, False])
+def test_every_ranks_share_of_a_sharded_call_matches_the_reference_heads(golden, name, world, host_plan):
+    """One GPU computes, rank by rank, what each rank of a kv-head-sharded call would: 32, 64 and 128-148 partials per
+    row, i.e. every instantiation of the merge step (one warp per row with 32 slots; one CTA per row with four warps
+    x 16, four x 24 and eight x 24).  The heads of each share against the same heads of the reference's output."""
+    p = wl.baseline_problem(name)
+    ref = golden[f"{name}/out"]
+    hq = p.Hq // world
+    for rank in (0, world - 1):
+        part = p.shard(rank, world)
+        r = run_cabi(part, host_lengths="rows" if host_plan else None, stable_fragments=1 if host_plan else 0)
+        assert r.rc == 0 and r.status == 0
+        check_against(r.out, ref[:, rank * hq:(rank + 1) * hq], p.dtype, what=f"{name} rank {rank} of {world}")
